@@ -1,0 +1,85 @@
+// Sampling over float32 logits: greedy argmax and temperature (Gumbel-max) with a
+// counter-based generator, one block per row.  The generator is a function of
+// (seed, counter, vocabulary index) alone, so a request's draws do not depend on
+// what else is in the batch.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+    x ^= x >> 16;
+    x *= 0x7FEB352Du;
+    x ^= x >> 15;
+    x *= 0x846CA68Bu;
+    x ^= x >> 16;
+    return x;
+}
+
+// Uniform in (0,1) with 23 random bits, centred in its cell: (k + 0.5) / 2^23 is
+// exact in float32 and never 0 or 1.
+__device__ __forceinline__ float uniform_for(uint32_t key, uint32_t index) {
+    const uint32_t x = mix32((index + 0x165667B1u) ^ key);
+    return ((float)(x >> 9) + 0.5f) * (1.0f / 8388608.0f);
+}
+
+// temperature[m] == 0: argmax, ties to the lowest index.
+// temperature[m] > 0 : argmax_i (logit_i / T - log(-log u_i)).
+__global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
+                              const float* __restrict__ temperature, const uint32_t* __restrict__ seeds,
+                              const uint32_t* __restrict__ counters, int V) {
+    __shared__ float s_val[32];
+    __shared__ int s_idx[32];
+    const int m = blockIdx.x;
+    const float* row = logits + (size_t)m * V;
+    const float T = temperature ? temperature[m] : 0.f;
+    uint32_t key = 0;
+    if (T > 0.f) {
+        key = mix32(seeds[m] ^ 0x9E3779B9u);
+        key = mix32(key ^ mix32(counters[m] + 0x85EBCA6Bu));
+    }
+    const float inv_t = T > 0.f ? 1.0f / T : 1.0f;
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        float v = row[i];
+        if (T > 0.f) {
+            const float u = uniform_for(key, (uint32_t)i);
+            v = v * inv_t - logf(-logf(u));
+        }
+        if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { s_val[warp] = best; s_idx[warp] = best_i; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        best = lane < nw ? s_val[lane] : -INFINITY;
+        best_i = lane < nw ? s_idx[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+        }
+        // A row of NaNs or -inf leaves best_i untouched; report index 0 rather than garbage.
+        if (lane == 0) out[m] = best_i == 0x7fffffff ? 0 : best_i;
+    }
+}
+
+}  // namespace
+
+extern "C" int sb_sample(int* out, const float* logits, const float* temperature, const uint32_t* seeds,
+                         const uint32_t* counters, int M, int V, cudaStream_t stream) {
+    SB_REQUIRE(M >= 0 && V > 0, "sample: bad sizes M=%d V=%d", M, V);
+    SB_REQUIRE(temperature == nullptr || (seeds != nullptr && counters != nullptr),
+               "sample: temperature sampling needs seeds and counters");
+    if (M == 0) return 0;
+    sample_kernel<<<M, 1024, 0, stream>>>(out, logits, temperature, seeds, counters, V);
+    SB_LAUNCH_CHECK();
+}

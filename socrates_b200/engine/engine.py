@@ -1,0 +1,144 @@
+"""The Python entry point: a model folder in, generated tokens out.
+
+    engine = Engine("model_folder")            # config.json + model.safetensors
+    req = engine.submit([5, 17, 3])            # token ids, or text with a tokenizer
+    engine.run()
+    req.output                                 # generated token ids
+
+Shape and argument names follow the reference's Engine (model/inference_paged.py:54-108:
+model, tok, device, dtype, compile, max_batch, max_len, max_new_tokens, block_size,
+num_blocks; submit / run / req.output, :132-148, 231-251).  `model` is a folder here,
+`compile` switches the CUDA graphs of the decode step, and `token_budget` (new) bounds
+the tokens of one step.
+"""
+
+from __future__ import annotations
+
+import time
+from pathlib import Path
+from typing import List, Optional, Sequence, Union
+
+import torch
+
+from ..cache import CacheManager
+from ..config import EngineConfig, load_config
+from ..kernels import require_kernels
+from ..sampling import SamplingParams
+from ..weights import load_weights
+from .model import Model
+from .runner import ModelRunner, SamplingArgs, StepEntry
+from .scheduler import QueueFull, Request, Scheduler, TooLong
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def resolve_dtype(dtype) -> torch.dtype:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"dtype must be bfloat16 or float32, not {dtype!r}") from None
+
+
+def build_model(model_dir, dtype: torch.dtype, device):
+    """(configuration, Model with its weights bound) of a model folder."""
+    config = load_config(model_dir)
+    model = Model(config.plan())
+    tensors = load_weights(model_dir, model.parameters(), dtype, device)
+    model.bind(tensors, dtype)
+    return config, model
+
+
+class Engine:
+    def __init__(self, model: Union[str, Path], tok=None, device: str = "cuda:0", dtype="bfloat16",
+                 compile: bool = True, max_batch: int = 64, max_len: int = 8192,
+                 max_new_tokens: int = 1024, block_size: int = 16, num_blocks: Optional[int] = None,
+                 token_budget: int = 2048, max_queue: Optional[int] = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("socrates_b200.Engine needs a CUDA device; there is no CPU path")
+        require_kernels()                      # fail at start-up, not on the first step
+        self.config = EngineConfig(max_batch=max_batch, max_len=max_len, max_new_tokens=max_new_tokens,
+                                   block_size=block_size, num_blocks=num_blocks,
+                                   token_budget=max(token_budget, max_batch), max_queue=max_queue,
+                                   dtype="float32" if resolve_dtype(dtype) == torch.float32 else "bfloat16",
+                                   compile=compile)
+        self.config.validate()
+        self.device = torch.device(device)
+        self.dtype = resolve_dtype(dtype)
+        torch.cuda.set_device(self.device)
+        self.model_config, self.model = build_model(model, self.dtype, self.device)
+        self.tok = tok
+        self.max_batch, self.max_len, self.max_new_tokens = max_batch, max_len, max_new_tokens
+
+        self.cache = CacheManager(self.model.cache_needs(), max_rows=max_batch, max_len=max_len,
+                                  page_size=block_size, num_pages=self.config.pool_blocks,
+                                  dtype=self.dtype, device=self.device)
+        self.runner = ModelRunner(self.model, self.cache, self.dtype, self.device,
+                                  max_tokens=self.config.token_budget, max_seqs=max_batch,
+                                  use_graphs=compile)
+        stop = set(getattr(self.model_config, "eos_token_ids", ()) or ())
+        if tok is not None:
+            stop |= set(getattr(tok, "all_special_ids", ()) or ())
+        self.scheduler = Scheduler(self.cache, max_batch, max_len, self.config.token_budget,
+                                   self.config.queue_limit, stop)
+        self.steps = 0
+
+    # ------------------------------------------------------------------ requests
+    def submit(self, prompt: Union[str, Sequence[int]], max_new_tokens: Optional[int] = None,
+               temperature: float = 0.0, seed: int = 0) -> Request:
+        """Queue a prompt (token ids, or text if the engine has a tokenizer).
+        Raises QueueFull or TooLong as the reference does (model/inference_paged.py:132-148)."""
+        text = None
+        if isinstance(prompt, str):
+            if self.tok is None:
+                raise ValueError("a text prompt needs a tokenizer (Engine(..., tok=...)); pass token ids instead")
+            text = prompt
+            templ = self.tok.apply_chat_template(
+                [{"role": "user", "content": prompt}], tokenize=False, add_generation_prompt=True,
+                enable_thinking=False)
+            enc = self.tok(templ)
+            ids = enc.input_ids[0] if isinstance(enc.input_ids[0], (list, tuple)) else list(enc.input_ids)
+            ids = [int(i) for i in ids]
+        else:
+            ids = [int(i) for i in prompt]
+        vocab = self.model.plan.vocab_size
+        for t in ids:
+            if not 0 <= t < vocab:
+                raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
+        req = Request(ids=ids, max_new_tokens=max_new_tokens or self.max_new_tokens,
+                      sampling=SamplingParams(float(temperature), int(seed)), prompt=text)
+        return self.scheduler.submit(req)
+
+    # ------------------------------------------------------------------ stepping
+    def step(self) -> bool:
+        """Plan and run one step; False when there was nothing to run."""
+        plan = self.scheduler.plan()
+        if plan is None:
+            return False
+        entries = [StepEntry(e.row, [e.request.token_at(i) for i in range(e.start, e.start + e.count)],
+                             e.start, [e.count - 1] if e.samples else [])
+                   for e in plan.entries]
+        args = [SamplingArgs(t, s, c) for (t, s, c) in self.scheduler.sampling_args(plan)]
+        result = self.runner.step(entries, args)
+        tokens = result.tokens.tolist() if result.tokens is not None else []   # the step's one read-back
+        self.scheduler.complete(plan, tokens)
+        self.steps += 1
+        return True
+
+    def run(self) -> None:
+        """Until every submitted request is finished (model/inference_paged.py:231-237)."""
+        while self.scheduler.has_work():
+            if not self.step():
+                if self.scheduler.has_work():
+                    raise RuntimeError("the scheduler has requests but could plan no step")
+
+    def generate(self, prompts: Sequence[Union[str, Sequence[int]]], max_new_tokens: Optional[int] = None,
+                 temperature: float = 0.0, seed: int = 0) -> List[List[int]]:
+        """Submit, run, and return the generated ids of each prompt, in order.
+        Request i samples with seed + i."""
+        reqs = [self.submit(p, max_new_tokens, temperature, seed + i) for i, p in enumerate(prompts)]
+        self.run()
+        return [r.output for r in reqs]
+
+
+__all__ = ["Engine", "Request", "QueueFull", "TooLong", "build_model", "resolve_dtype"]

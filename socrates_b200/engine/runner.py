@@ -1,0 +1,221 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+`ModelRunner.step(entries)` runs only the tokens it is given, as one flat batch, from
+the cache that earlier steps left, and returns float32 logits at the wanted places.
+Portions of prompts and single decode tokens mix freely and a prompt may be cut
+anywhere.  The reference's forward takes a rectangle instead, either one whole prompt
+or n rows of one token (model/qwen/qwen_kv_paged.py:207-224).
+
+Host and device: the step's integers are written into one pinned buffer and reach the
+device in one copy; nothing is read back inside the step.  A step in which every
+request brings one token is recorded once per batch width into a CUDA graph and
+replayed afterwards (the reference compiles one graph per width with
+torch.compile(mode="reduce-overhead"), model/inference_paged.py:99-130).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..kernels import ops
+from .context import Buffers, StepContext
+from .model import Model
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request: `tokens` start at position `start` of cache row
+    `row`; `want` lists the places among these tokens whose logits are asked for."""
+    row: int
+    tokens: Sequence[int]
+    start: int
+    want: Sequence[int] = ()
+
+
+@dataclass
+class SamplingArgs:
+    """How to turn one wanted row of logits into a token (see socrates_b200.sampling)."""
+    temperature: float = 0.0
+    seed: int = 0
+    counter: int = 0
+
+
+@dataclass
+class StepResult:
+    logits: Optional[torch.Tensor]          # float32 [wanted, vocab] on the device, or None
+    tokens: Optional[torch.Tensor] = None   # int32 [wanted] on the device when sampling was asked for
+    num_tokens: int = 0
+
+
+class _Layout:
+    """Offsets of the step's integer arrays inside the staging buffer."""
+
+    def __init__(self, T: int, R: int):
+        self.T, self.R = T, R
+        self.ids, self.pos, self.rows, self.logit = 0, T, 2 * T, 3 * T
+        self.temp, self.seed, self.counter = 4 * T, 5 * T, 6 * T
+        self.seq_starts = 7 * T
+        self.seq_rows = self.seq_starts + R + 1
+        self.seq_first = self.seq_rows + R
+        self.total = self.seq_first + R
+
+
+class ModelRunner:
+    def __init__(self, model: Model, cache: CacheManager, dtype: torch.dtype, device,
+                 max_tokens: int, max_seqs: int, use_graphs: bool = True):
+        self.model, self.cache = model, cache
+        self.dtype, self.device = dtype, torch.device(device)
+        self.max_tokens, self.max_seqs = max_tokens, max_seqs
+        self.vocab = model.plan.vocab_size
+        self.buffers = Buffers(max_tokens, self.device)
+        self.layout = _Layout(max_tokens, max_seqs)
+        self.dev_meta = torch.zeros(self.layout.total, dtype=torch.int32, device=self.device)
+        self._staging = [[torch.zeros(self.layout.total, dtype=torch.int32).pin_memory(), None]
+                         for _ in range(4)]
+        self._next = 0
+        self.sampled = torch.zeros(max_tokens, dtype=torch.int32, device=self.device)
+        self.use_graphs = use_graphs and model.supports_graph
+        self._graphs: Dict[Tuple[int, int, bool], Tuple[torch.cuda.CUDAGraph, Optional[torch.Tensor]]] = {}
+        self._eager_decode_done: set = set()
+        self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.launches = 0           # steps run; graph replays counted separately
+        self.graph_replays = 0
+
+    # ------------------------------------------------------------------ staging
+    def _stage(self) -> Tuple[torch.Tensor, int]:
+        i = self._next
+        self._next = (i + 1) % len(self._staging)
+        buf, ev = self._staging[i]
+        if ev is not None:
+            ev.synchronize()
+        return buf, i
+
+    def _fill(self, entries: Sequence[StepEntry], sampling) -> Tuple[int, int, int, bool, int]:
+        L = self.layout
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        if len(entries) > self.max_seqs:
+            raise ValueError(f"{len(entries)} requests exceed the step limit of {self.max_seqs}")
+        ids: List[int] = []
+        pos: List[int] = []
+        rows: List[int] = []
+        logit: List[int] = []
+        starts = [0]
+        seen = set()
+        all_decode = True
+        max_ctx = 0
+        for e in entries:
+            n = len(e.tokens)
+            if n < 1:
+                raise ValueError("an entry needs at least one token")
+            if e.row in seen:
+                raise ValueError(f"row {e.row} appears twice in one step")
+            seen.add(e.row)
+            if not 0 <= e.row < self.cache.max_rows:
+                raise ValueError(f"row {e.row} is outside the cache")
+            if e.start != self.cache.lengths[e.row]:
+                raise ValueError(f"row {e.row} holds {self.cache.lengths[e.row]} tokens; "
+                                 f"the entry starts at {e.start}")
+            if e.start + n > self.cache.max_len:
+                raise ValueError(f"row {e.row} would exceed {self.cache.max_len} tokens")
+            for t in e.tokens:
+                if not 0 <= t < self.vocab:
+                    raise ValueError(f"token id {t} is outside the vocabulary of {self.vocab}")
+            base = len(ids)
+            ids.extend(int(t) for t in e.tokens)
+            pos.extend(range(e.start, e.start + n))
+            rows.extend([e.row] * n)
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"wanted place {w} is outside the entry's {n} tokens")
+                logit.append(base + w)
+            starts.append(len(ids))
+            all_decode &= n == 1
+            max_ctx = max(max_ctx, e.start + n)
+        N, M, R = len(ids), len(logit), len(entries)
+        if N > self.max_tokens:
+            raise ValueError(f"{N} tokens exceed the step limit of {self.max_tokens}")
+        if sampling is not None and len(sampling) != M:
+            raise ValueError(f"{len(sampling)} sampling entries for {M} wanted logits")
+
+        buf, slot = self._stage()
+        buf[L.ids:L.ids + N] = torch.tensor(ids, dtype=torch.int32)
+        buf[L.pos:L.pos + N] = torch.tensor(pos, dtype=torch.int32)
+        buf[L.rows:L.rows + N] = torch.tensor(rows, dtype=torch.int32)
+        if M:
+            buf[L.logit:L.logit + M] = torch.tensor(logit, dtype=torch.int32)
+        if sampling is not None and M:
+            buf[L.temp:L.temp + M] = torch.tensor([s.temperature for s in sampling],
+                                                  dtype=torch.float32).view(torch.int32)
+            buf[L.seed:L.seed + M] = torch.tensor([_as_i32(s.seed) for s in sampling], dtype=torch.int32)
+            buf[L.counter:L.counter + M] = torch.tensor([_as_i32(s.counter) for s in sampling],
+                                                        dtype=torch.int32)
+        buf[L.seq_starts:L.seq_starts + R + 1] = torch.tensor(starts, dtype=torch.int32)
+        buf[L.seq_rows:L.seq_rows + R] = torch.tensor([e.row for e in entries], dtype=torch.int32)
+        buf[L.seq_first:L.seq_first + R] = torch.tensor([e.start for e in entries], dtype=torch.int32)
+        self.dev_meta.copy_(buf, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._staging[slot][1] = ev
+        return N, M, R, all_decode, max_ctx
+
+    def _context(self, N: int, M: int, R: int, all_decode: bool, max_ctx: int, host_batch) -> StepContext:
+        L, m = self.layout, self.dev_meta
+        return StepContext(
+            self.dtype, self.device, self.buffers, N, R,
+            token_ids=m[L.ids:L.ids + N], positions=m[L.pos:L.pos + N], token_rows=m[L.rows:L.rows + N],
+            seq_starts=m[L.seq_starts:L.seq_starts + R + 1], seq_rows=m[L.seq_rows:L.seq_rows + R],
+            seq_first_pos=m[L.seq_first:L.seq_first + R],
+            logit_index=m[L.logit:L.logit + M] if M else None,
+            all_decode=all_decode, max_context=max_ctx, host_batch=host_batch, num_sms=self.num_sms)
+
+    def _run(self, ctx: StepContext, M: int, sample: bool):
+        logits = self.model.forward(ctx, self.cache)
+        tokens = None
+        if sample and M:
+            L, m = self.layout, self.dev_meta
+            tokens = self.sampled[:M]
+            ops.sample(tokens, logits, m[L.temp:L.temp + M].view(torch.float32),
+                       m[L.seed:L.seed + M], m[L.counter:L.counter + M])
+        return logits, tokens
+
+    # ------------------------------------------------------------------ the step
+    @torch.no_grad()
+    def step(self, entries: Sequence[StepEntry],
+             sampling: Optional[Sequence[SamplingArgs]] = None) -> StepResult:
+        """Run one batch.  The caller has reserved pages for every entry
+        (`cache.reserve(row, start + len(tokens))`) and commits the new lengths after."""
+        self.cache.flush()
+        N, M, R, all_decode, max_ctx = self._fill(entries, sampling)
+        sample = sampling is not None
+        self.launches += 1
+        if self.use_graphs and all_decode and M == N:
+            key = (N, sample)
+            if key in self._graphs:
+                graph, logits, tokens = self._graphs[key]
+                graph.replay()
+                self.graph_replays += 1
+                return StepResult(logits, tokens, N)
+            if key in self._eager_decode_done:
+                ctx = self._context(N, M, R, True, self.cache.max_len, None)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    logits, tokens = self._run(ctx, M, sample)
+                self._graphs[key] = (graph, logits, tokens)
+                graph.replay()
+                self.graph_replays += 1
+                return StepResult(logits, tokens, N)
+            self._eager_decode_done.add(key)
+            max_ctx = self.cache.max_len     # the same launch shapes the graph will record
+        ctx = self._context(N, M, R, all_decode, max_ctx, entries)
+        logits, tokens = self._run(ctx, M, sample)
+        return StepResult(logits, tokens, N)
+
+
+def _as_i32(x: int) -> int:
+    x &= 0xFFFFFFFF
+    return x - (1 << 32) if x >= (1 << 31) else x

@@ -1,0 +1,200 @@
+"""Typed Python entry points of the CUDA kernels.
+
+Each function checks device, dtype, shape and contiguity of its tensors, then calls
+the C entry point with raw pointers on torch's current stream.  Outputs are written
+into tensors the caller passes: nothing here allocates, so every call can be
+recorded in a CUDA graph.  (The reference performs the same checks in C++,
+model/kernels/csrc/ops.cpp:29-72.)
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .library import KernelError, check, library
+
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"dtype {dtype} is not supported; float32 and bfloat16 are") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _want(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise KernelError(f"{name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
+
+
+def embed(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
+    """out[n, :] = float32(table[ids[n], :]); out float32 [N, d], ids int32 [N]."""
+    V, d = table.shape
+    N = ids.numel()
+    _want(table, "table")
+    _want(ids, "ids", torch.int32)
+    _want(out, "out", torch.float32, (N, d))
+    lib = library()
+    check(lib, lib.sb_embed(_ptr(out), _ptr(table), _ptr(ids), N, d, V, _code(table.dtype), _stream()),
+          "embed")
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor,
+                out: torch.Tensor, eps: float, row_index: Optional[torch.Tensor] = None) -> None:
+    """residual += sum(delta, 0); out = rmsnorm(residual) * gain.
+
+    residual float32 [N, d]; delta float32 [S, N, d] or None; gain float32 [d];
+    out [M, d] in the model dtype, M = len(row_index) or N.  With row_index only the
+    named rows are normed and the residual is left as it is.
+    """
+    N, d = residual.shape
+    _want(residual, "residual", torch.float32)
+    _want(gain, "gain", torch.float32, (d,))
+    S, stride = 0, 0
+    if delta is not None:
+        _want(delta, "delta", torch.float32)
+        if delta.dim() != 3 or delta.shape[1:] != (N, d):
+            raise KernelError(f"delta must be [S, {N}, {d}], got {tuple(delta.shape)}")
+        S, stride = delta.shape[0], N * d
+    M = N
+    if row_index is not None:
+        _want(row_index, "row_index", torch.int32)
+        M = row_index.numel()
+    _want(out, "out", None, (M, d))
+    lib = library()
+    check(lib, lib.sb_add_rmsnorm(_ptr(residual), _ptr(delta), S, stride, _ptr(gain), _ptr(out),
+                                  _ptr(row_index), M, d, float(eps), _code(out.dtype), _stream()),
+          "add_rmsnorm")
+
+
+def qk_norm_rope_kvwrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[torch.Tensor],
+                         v_pool: Optional[torch.Tensor], q_gain: Optional[torch.Tensor],
+                         k_gain: Optional[torch.Tensor], inv_freq: torch.Tensor, rotary_dim: int,
+                         positions: torch.Tensor, token_rows: torch.Tensor, block_table: torch.Tensor,
+                         eps: float, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+    """Per-head norm, rotation and paged KV write for N tokens.
+
+    qkv [N, (Hq+2Hkv)*D]; q_out [N, Hq*D]; pools [pages, Hkv, BS, D] (None: the keys
+    and values of this step are not stored, the layer reads another layer's cache).
+    """
+    N = qkv.shape[0]
+    Hq, Hkv, D = num_heads, num_kv_heads, head_dim
+    _want(qkv, "qkv", None, (N, (Hq + 2 * Hkv) * D))
+    _want(q_out, "q_out", qkv.dtype, (N, Hq * D))
+    _want(positions, "positions", torch.int32, (N,))
+    _want(token_rows, "token_rows", torch.int32, (N,))
+    _want(block_table, "block_table", torch.int32)
+    _want(inv_freq, "inv_freq", torch.float32)
+    if inv_freq.numel() < rotary_dim // 2:
+        raise KernelError(f"inv_freq has {inv_freq.numel()} entries for rotary_dim {rotary_dim}")
+    write_kv = k_pool is not None
+    page_size = 1
+    if write_kv:
+        _want(k_pool, "k_pool", qkv.dtype)
+        _want(v_pool, "v_pool", qkv.dtype, k_pool.shape)
+        if k_pool.dim() != 4 or k_pool.shape[1] != Hkv or k_pool.shape[3] != D:
+            raise KernelError(f"pools must be [pages, {Hkv}, page_size, {D}], got {tuple(k_pool.shape)}")
+        page_size = k_pool.shape[2]
+    for g, nm in ((q_gain, "q_gain"), (k_gain, "k_gain")):
+        if g is not None:
+            _want(g, nm, torch.float32, (D,))
+    lib = library()
+    check(lib, lib.sb_qk_norm_rope_kvwrite(
+        _ptr(qkv), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(q_gain), _ptr(k_gain), _ptr(inv_freq),
+        rotary_dim, _ptr(positions), _ptr(token_rows), _ptr(block_table), block_table.shape[1],
+        page_size, float(eps), Hq, Hkv, D, N, int(write_kv), _code(qkv.dtype), _stream()),
+        "qk_norm_rope_kvwrite")
+
+
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
+    """out[n, f] = gate_up[n, F + f] * silu(gate_up[n, f])."""
+    N, F2 = gate_up.shape
+    _want(gate_up, "gate_up")
+    _want(out, "out", gate_up.dtype, (N, F2 // 2))
+    lib = library()
+    check(lib, lib.sb_silu_mul(_ptr(out), _ptr(gate_up), N, F2 // 2, _code(out.dtype), _stream()),
+          "silu_mul")
+
+
+def sample(out: torch.Tensor, logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+           seeds: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None) -> None:
+    """out[m] = argmax(logits[m]) where temperature[m] == 0 (or temperature is None),
+    else a draw from softmax(logits[m] / temperature[m]) fixed by (seeds[m], counters[m])."""
+    M, V = logits.shape
+    _want(logits, "logits", torch.float32)
+    _want(out, "out", torch.int32, (M,))
+    if temperature is not None:
+        _want(temperature, "temperature", torch.float32, (M,))
+        _want(seeds, "seeds", torch.int32, (M,))
+        _want(counters, "counters", torch.int32, (M,))
+    lib = library()
+    check(lib, lib.sb_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(seeds), _ptr(counters),
+                             M, V, _stream()), "sample")
+
+
+def gemm_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, splits: int = 1) -> None:
+    """out = a @ w.T on the CUDA cores with float32 accumulation.
+
+    a [M, K], w [N, K]; out [M, N], or float32 [splits, M, N] partial sums.
+    """
+    M, K = a.shape
+    N = w.shape[0]
+    _want(a, "a")
+    _want(w, "w", None, (N, K))
+    if splits == 1 and out.dim() == 2:
+        _want(out, "out", None, (M, N))
+    else:
+        _want(out, "out", torch.float32, (splits, M, N))
+    lib = library()
+    check(lib, lib.sb_gemm_simt(_ptr(out), _ptr(a), _ptr(w), M, N, K, _code(a.dtype), _code(w.dtype),
+                                _code(out.dtype), splits, _stream()), "gemm_simt")
+
+
+def attention_simt(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                   block_table: torch.Tensor, token_rows: torch.Tensor, positions: torch.Tensor,
+                   num_heads: int, scale: float, window: int = 0, num_partitions: int = 1,
+                   part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> None:
+    """Paged causal attention, one query per token, on the CUDA cores.
+
+    q, out [N, Hq*D]; pools [pages, Hkv, BS, D]; block_table int32 [rows, W];
+    window 0 = all keys.  Scratch for num_partitions > 1: part_o float32 with at least
+    N*Hq*NP*D elements, part_ml with N*Hq*NP*2.
+    """
+    N = q.shape[0]
+    pages, Hkv, BS, D = k_pool.shape
+    Hq = num_heads
+    _want(q, "q", k_pool.dtype, (N, Hq * D))
+    _want(out, "out", q.dtype, (N, Hq * D))
+    _want(k_pool, "k_pool")
+    _want(v_pool, "v_pool", k_pool.dtype, k_pool.shape)
+    _want(block_table, "block_table", torch.int32)
+    _want(token_rows, "token_rows", torch.int32, (N,))
+    _want(positions, "positions", torch.int32, (N,))
+    if num_partitions > 1:
+        _want(part_o, "part_o", torch.float32)
+        _want(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < N * Hq * num_partitions * D or part_ml.numel() < N * Hq * num_partitions * 2:
+            raise KernelError("attention scratch buffers are too small")
+    lib = library()
+    check(lib, lib.sb_attention_simt(
+        _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+        block_table.shape[1], _ptr(token_rows), _ptr(positions), N, Hq, Hkv, D, BS, int(window),
+        float(scale), num_partitions, _code(q.dtype), _stream()), "attention")

@@ -1,0 +1,46 @@
+"""SwiGLU feed-forward: down(up(x) * silu(gate(x))), no bias
+(model/qwen/qwen_kv_cont.py:250-266).  gate and up are one matrix product here (the
+weights are concatenated when they are bound); silu(z) = z * sigmoid(z) in float32."""
+
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from ..kernels import ops
+from .base import Branch, ParamSpec, Part, register_part
+from .linear import Linear
+
+
+class SwiGLU(Part):
+    def __init__(self, spec, name):
+        super().__init__(spec, name)
+        self.hidden = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.gate_up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        n = self.name
+        return {
+            n + "gate_proj.weight": ParamSpec((self.inter, self.hidden)),
+            n + "up_proj.weight": ParamSpec((self.inter, self.hidden)),
+            n + "down_proj.weight": ParamSpec((self.hidden, self.inter)),
+        }
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype) -> None:
+        n = self.name
+        self.gate_up = Linear(torch.cat([tensors[n + "gate_proj.weight"],
+                                         tensors[n + "up_proj.weight"]], dim=0))
+        self.down = Linear(tensors[n + "down_proj.weight"])
+
+    def forward(self, ctx, x: torch.Tensor) -> Branch:
+        N = x.shape[0]
+        gu = self.gate_up(ctx, x, "gate_up")
+        act = ctx.buffers.take("act", N, (self.inter,), ctx.dtype)
+        ops.silu_mul(act, gu)
+        return Branch(self.down(ctx, act, "branch", out="partial"))
+
+
+register_part("feed_forward", "swiglu", SwiGLU)

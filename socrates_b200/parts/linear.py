@@ -1,0 +1,37 @@
+"""y = x W^T for a weight matrix [out, in] (torch.nn.Linear layout, no bias).
+
+`Linear` chooses the kernel: the float32 path and shapes the tensor-core kernel does
+not take run on the CUDA cores (`gemm_simt`); bfloat16 runs on the tcgen05 kernel when
+it is loaded.  The output is the model dtype `[M, N]`, float32 `[M, N]` (logits), or
+float32 partial sums `[S, M, N]` for a branch that the next norm adds to the residual.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor):
+        if weight.dim() != 2:
+            raise ValueError(f"a weight matrix has two dims, got {tuple(weight.shape)}")
+        self.weight = weight.contiguous()
+        self.out_features, self.in_features = weight.shape
+
+    def __call__(self, ctx, x: torch.Tensor, buffer: str, out: str = "model") -> torch.Tensor:
+        """`out`: "model" -> [M, N] in the model dtype; "float32" -> [M, N] float32;
+        "partial" -> float32 [S, M, N]."""
+        M = x.shape[0]
+        N = self.out_features
+        if out == "model":
+            y = ctx.buffers.take(buffer, M, (N,), ctx.dtype)
+        elif out == "float32":
+            y = ctx.buffers.take(buffer, M, (N,), torch.float32)
+        elif out == "partial":
+            y = ctx.buffers.take_flat(buffer, M * N, torch.float32).view(1, M, N)
+        else:
+            raise ValueError(out)
+        ctx.gemm(y, x, self.weight)
+        return y

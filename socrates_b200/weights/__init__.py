@@ -1,0 +1,4 @@
+from .loader import WeightsError, load_weights, place
+from .random_init import random_tensors, write_model_folder
+
+__all__ = ["WeightsError", "load_weights", "place", "random_tensors", "write_model_folder"]
