@@ -24,7 +24,7 @@ from ..cache import CacheManager
 from ..config import EngineConfig, load_config
 from ..kernels import require_kernels
 from ..sampling import SamplingParams
-from ..weights import load_weights
+from ..weights import load_weights, random_tensors_on_device
 from .model import Model
 from .runner import ModelRunner, SamplingArgs, StepEntry
 from .scheduler import QueueFull, Request, Scheduler, TooLong
@@ -49,8 +49,15 @@ def build_model(model_dir, dtype: torch.dtype, device):
     return config, model
 
 
+def build_random_model(config, seed: int, dtype: torch.dtype, device):
+    """(configuration, Model) with random weights drawn on the device (no folder)."""
+    model = Model(config.plan())
+    model.bind(random_tensors_on_device(model.parameters(), seed, dtype, device), dtype)
+    return config, model
+
+
 class Engine:
-    def __init__(self, model: Union[str, Path], tok=None, device: str = "cuda:0", dtype="bfloat16",
+    def __init__(self, model, tok=None, device: str = "cuda:0", dtype="bfloat16",
                  compile: bool = True, max_batch: int = 64, max_len: int = 8192,
                  max_new_tokens: int = 1024, block_size: int = 16, num_blocks: Optional[int] = None,
                  token_budget: int = 2048, max_queue: Optional[int] = None):
@@ -66,7 +73,10 @@ class Engine:
         self.device = torch.device(device)
         self.dtype = resolve_dtype(dtype)
         torch.cuda.set_device(self.device)
-        self.model_config, self.model = build_model(model, self.dtype, self.device)
+        if isinstance(model, (str, Path)):
+            self.model_config, self.model = build_model(model, self.dtype, self.device)
+        else:
+            self.model_config, self.model = model          # (configuration, Model with weights bound)
         self.tok = tok
         self.max_batch, self.max_len, self.max_new_tokens = max_batch, max_len, max_new_tokens
 
@@ -141,4 +151,5 @@ class Engine:
         return [r.output for r in reqs]
 
 
-__all__ = ["Engine", "Request", "QueueFull", "TooLong", "build_model", "resolve_dtype"]
+__all__ = ["Engine", "Request", "QueueFull", "TooLong", "build_model", "build_random_model",
+           "resolve_dtype"]

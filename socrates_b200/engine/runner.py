@@ -22,6 +22,7 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..kernels import ops
+from ..kernels.library import Counters
 from .context import Buffers, StepContext
 from .model import Model
 
@@ -82,8 +83,10 @@ class ModelRunner:
         self._graphs: Dict[Tuple[int, int, bool], Tuple[torch.cuda.CUDAGraph, Optional[torch.Tensor]]] = {}
         self._eager_decode_done: set = set()
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        self.launches = 0           # steps run; graph replays counted separately
+        self.steps_run = 0
         self.graph_replays = 0
+        self.kernel_launches = 0    # kernels launched by steps, replays of recorded graphs included
+        self._graph_kernels: Dict[Tuple[int, bool], int] = {}
 
     # ------------------------------------------------------------------ staging
     def _stage(self) -> Tuple[torch.Tensor, int]:
@@ -183,6 +186,14 @@ class ModelRunner:
                        m[L.seed:L.seed + M], m[L.counter:L.counter + M])
         return logits, tokens
 
+    def prepare(self, entries: Sequence[StepEntry],
+                sampling: Optional[Sequence[SamplingArgs]] = None) -> StepContext:
+        """Copy the step's integers to the device and return the context the parts see.
+        `step` does this itself; tests of single parts call it to run a part alone."""
+        self.cache.flush()
+        N, M, R, all_decode, max_ctx = self._fill(entries, sampling)
+        return self._context(N, M, R, all_decode, max_ctx, entries)
+
     # ------------------------------------------------------------------ the step
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry],
@@ -192,27 +203,29 @@ class ModelRunner:
         self.cache.flush()
         N, M, R, all_decode, max_ctx = self._fill(entries, sampling)
         sample = sampling is not None
-        self.launches += 1
+        self.steps_run += 1
         if self.use_graphs and all_decode and M == N:
             key = (N, sample)
+            if key not in self._graphs and key in self._eager_decode_done:
+                ctx = self._context(N, M, R, True, self.cache.max_len, None)
+                graph = torch.cuda.CUDAGraph()
+                before = Counters.launches
+                with torch.cuda.graph(graph):
+                    logits, tokens = self._run(ctx, M, sample)
+                self._graph_kernels[key] = Counters.launches - before
+                self._graphs[key] = (graph, logits, tokens)
             if key in self._graphs:
                 graph, logits, tokens = self._graphs[key]
                 graph.replay()
                 self.graph_replays += 1
-                return StepResult(logits, tokens, N)
-            if key in self._eager_decode_done:
-                ctx = self._context(N, M, R, True, self.cache.max_len, None)
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    logits, tokens = self._run(ctx, M, sample)
-                self._graphs[key] = (graph, logits, tokens)
-                graph.replay()
-                self.graph_replays += 1
+                self.kernel_launches += self._graph_kernels[key]
                 return StepResult(logits, tokens, N)
             self._eager_decode_done.add(key)
             max_ctx = self.cache.max_len     # the same launch shapes the graph will record
         ctx = self._context(N, M, R, all_decode, max_ctx, entries)
+        before = Counters.launches
         logits, tokens = self._run(ctx, M, sample)
+        self.kernel_launches += Counters.launches - before
         return StepResult(logits, tokens, N)
 
 

@@ -65,7 +65,14 @@ def library_path() -> Optional[str]:
     return _lib_path
 
 
-def check(lib: ctypes.CDLL, code: int, what: str) -> None:
+class Counters:
+    """Kernels launched through the entry points since import.  A launch recorded into a
+    CUDA graph counts once here; every replay launches the same kernels again."""
+    launches = 0
+
+
+def check(lib: ctypes.CDLL, code: int, what: str, kernels: int = 1) -> None:
+    Counters.launches += kernels
     if code != 0:
         msg = lib.sb_last_error().decode(errors="replace")
         raise KernelError(f"{what}: {msg} (code {code})")

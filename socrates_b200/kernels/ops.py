@@ -197,4 +197,5 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_p
     check(lib, lib.sb_attention_simt(
         _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
         block_table.shape[1], _ptr(token_rows), _ptr(positions), N, Hq, Hkv, D, BS, int(window),
-        float(scale), num_partitions, _code(q.dtype), _stream()), "attention")
+        float(scale), num_partitions, _code(q.dtype), _stream()), "attention",
+        kernels=2 if num_partitions > 1 else 1)

@@ -55,3 +55,20 @@ def write_model_folder(config, seed: int, out_dir, matrix_dtype: torch.dtype = t
     (out_dir / "config.json").write_text(json.dumps(config.to_dict(), indent=1))
     save_file(tensors, str(out_dir / "model.safetensors"))
     return out_dir
+
+
+def random_tensors_on_device(expected: Mapping[str, ParamSpec], seed: int, dtype: torch.dtype,
+                             device) -> Dict[str, torch.Tensor]:
+    """The same distributions drawn on the device, for models too large to draw on the
+    host in reasonable time (benchmarks).  Values differ from `random_tensors`."""
+    g = torch.Generator(device=device)
+    out: Dict[str, torch.Tensor] = {}
+    for i, (name, spec) in enumerate(expected.items()):
+        g.manual_seed(seed * 1000003 + i)
+        if spec.init == "gain":
+            out[name] = 1.0 + 0.1 * torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32)
+        else:
+            t = torch.empty(spec.shape, device=device, dtype=dtype)
+            t.normal_(0.0, 0.02, generator=g)
+            out[name] = t
+    return out

@@ -1,0 +1,157 @@
+"""Generation through the Python entry point against the plain implementation."""
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from tiny_configs import CONFIGS, make_folder
+
+pytestmark = pytest.mark.gpu
+
+
+def engine_for(folder, dtype, **kw):
+    from socrates_b200 import Engine
+    args = dict(device="cuda:0", dtype=dtype, max_batch=4, max_len=512, max_new_tokens=8, block_size=16,
+                token_budget=64)
+    args.update(kw)
+    return Engine(str(folder), **args)
+
+
+def prompts_for(name, lengths, seed=3):
+    vocab = CONFIGS[name][0]["vocab_size"]
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(1, vocab, (n,), generator=g).tolist() for n in lengths]
+
+
+def check_teacher_forced(cfg, w, prompt, output, margin, temperature=0.0, seed=0):
+    """Every produced token must be the plain implementation's choice given the tokens
+    before it, or lose to that choice by less than `margin` (a tie within rounding)."""
+    seq = list(prompt) + list(output)
+    logits = plain.logits(w, cfg, seq[:-1] if output else seq)
+    scale = float(logits.abs().max())
+    for i, tok in enumerate(output):
+        row = logits[len(prompt) - 1 + i]
+        if temperature > 0:
+            scores = plain.temperature_scores(row, temperature, seed, i)
+            gap = margin * scale / temperature
+        else:
+            scores, gap = row, margin * scale
+        best = int(torch.argmax(scores))
+        assert tok == best or float(scores[best] - scores[tok]) <= gap, (
+            f"token {i}: engine chose {tok}, plain chose {best}, "
+            f"score gap {float(scores[best] - scores[tok]):.3g} > {gap:.3g}")
+
+
+@pytest.mark.parametrize("dtype,margin", [("float32", 1e-4), ("bfloat16", 2e-2)])
+def test_greedy_config_a(tmp_path, dtype, margin):
+    """Tiny A: prompts of 5, 11 and 17 tokens, 8 new tokens each, greedy, 16-slot pages."""
+    folder = make_folder(tmp_path, "A")
+    cfg, w = plain.load_folder(folder)
+    ps = prompts_for("A", [5, 11, 17])
+    eng = engine_for(folder, dtype)
+    outs = eng.generate(ps, max_new_tokens=8)
+    assert all(len(o) == 8 for o in outs)
+    for p, o in zip(ps, outs):
+        check_teacher_forced(cfg, w, p, o, margin)
+    if dtype == "float32":
+        for p, o in zip(ps, outs):                     # free-running: exactly the plain greedy tokens
+            seq = list(p)
+            for t in o:
+                assert t == plain.greedy(plain.logits(w, cfg, seq)[-1])
+                seq.append(t)
+    assert eng.cache.free_pages() == [g.allocator.num_pages for g in eng.cache.groups]
+
+
+@pytest.mark.parametrize("dtype,margin", [("float32", 1e-4), ("bfloat16", 2e-2)])
+def test_temperature_config_b_portions_beside_decode(tmp_path, dtype, margin):
+    """Tiny B: prompts of 1, 16, 23 and 40 tokens cut into 8-token portions that share
+    steps with decoding rows; 6 new tokens at temperature 0.8, seeded."""
+    folder = make_folder(tmp_path, "B")
+    cfg, w = plain.load_folder(folder)
+    ps = prompts_for("B", [1, 16, 23, 40])
+    eng = engine_for(folder, dtype, token_budget=8, max_batch=4)
+    outs = eng.generate(ps, max_new_tokens=6, temperature=0.8, seed=100)
+    assert all(len(o) == 6 for o in outs)
+    for i, (p, o) in enumerate(zip(ps, outs)):
+        check_teacher_forced(cfg, w, p, o, margin, temperature=0.8, seed=100 + i)
+    again = engine_for(folder, dtype, token_budget=64, max_batch=2)
+    assert again.generate(ps, max_new_tokens=6, temperature=0.8, seed=100) == outs or dtype == "bfloat16"
+
+
+def test_long_decoding_float32(tmp_path):
+    """200 decode steps (the recorded CUDA graph path) across many page edges and, in
+    config B, far past the window."""
+    for name in ("A", "B"):
+        folder = make_folder(tmp_path / name, name)
+        cfg, w = plain.load_folder(folder)
+        p = prompts_for(name, [3])[0]
+        eng = engine_for(folder, "float32", max_new_tokens=200)
+        out = eng.generate([p], max_new_tokens=200)[0]
+        assert len(out) == 200
+        assert eng.runner.graph_replays >= 190
+        check_teacher_forced(cfg, w, p, out, 1e-4)
+
+
+def test_graphs_and_eager_agree(tmp_path):
+    folder = make_folder(tmp_path, "A")
+    ps = prompts_for("A", [9, 30, 2])
+    a = engine_for(folder, "bfloat16", compile=True).generate(ps, max_new_tokens=40)
+    b = engine_for(folder, "bfloat16", compile=False).generate(ps, max_new_tokens=40)
+    assert a == b
+
+
+def test_few_pages_preemption_keeps_outputs(tmp_path):
+    """A pool too small for all requests at once: some are preempted and recomputed, and
+    every request still gets the tokens it gets when it runs alone."""
+    folder = make_folder(tmp_path, "B")
+    ps = prompts_for("B", [40, 25, 33, 8, 50, 12])
+    alone = [engine_for(folder, "float32", max_batch=1).generate([p], max_new_tokens=30)[0] for p in ps]
+    eng = engine_for(folder, "float32", max_batch=4, num_blocks=9, max_len=96, token_budget=16)
+    reqs = [eng.submit(p, max_new_tokens=30) for p in ps]
+    while eng.scheduler.has_work():
+        assert eng.step()
+        eng.scheduler.check()
+    assert [r.output for r in reqs] == alone
+    assert eng.scheduler.preemptions > 0
+    assert eng.cache.free_pages() == [9, 9]
+
+
+def test_first_tokens_of_a_sequence(tmp_path):
+    """Positions 0 and 1 alone: one-token and two-token prompts, and a first portion of one token."""
+    from socrates_b200.engine.runner import StepEntry
+    folder = make_folder(tmp_path, "A")
+    cfg, w = plain.load_folder(folder)
+    eng = engine_for(folder, "float32")
+    ids = [7, 201, 33]
+    ref = plain.logits(w, cfg, ids)
+    cache, runner = eng.cache, eng.runner
+    cache.assign(0)
+    cache.reserve(0, 1)
+    l0 = runner.step([StepEntry(0, ids[:1], 0, [0])]).logits.cpu().double()
+    cache.commit(0, 1)
+    cache.reserve(0, 3)
+    l12 = runner.step([StepEntry(0, ids[1:], 1, [0, 1])]).logits.cpu().double()
+    cache.commit(0, 3)
+    cache.release(0)
+    scale = float(ref.abs().max())
+    assert float((l0[0] - ref[0]).abs().max()) / scale < 1e-4
+    assert float((l12 - ref[1:]).abs().max()) / scale < 1e-4
+
+
+def test_entry_point_guards(tmp_path):
+    from socrates_b200 import Engine, TooLong
+    folder = make_folder(tmp_path, "A")
+    eng = engine_for(folder, "bfloat16", max_len=64)
+    with pytest.raises(TooLong):
+        eng.submit(list(range(1, 60)), max_new_tokens=10)
+    with pytest.raises(ValueError):
+        eng.submit([1, 2, 999])                        # outside the vocabulary
+    with pytest.raises(ValueError):
+        eng.submit("text without a tokenizer")
+    from socrates_b200.engine.tokenizer import ByteTokenizer
+    eng2 = Engine(str(folder), tok=ByteTokenizer(256), max_batch=2, max_len=64, max_new_tokens=4)
+    r = eng2.submit("hi there")
+    eng2.run()
+    assert r.done and len(r.output) <= 4 and 0 not in r.output
+    with pytest.raises(ValueError):
+        Engine(str(folder), dtype="float16")

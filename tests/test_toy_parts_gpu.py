@@ -1,0 +1,194 @@
+"""A mixer with state of its own, defined here, is registered, built and stepped
+without any change to the framework: the cache manager gives it a state slot, the
+step function carries the state across portions, and the model runs it in a layer of
+its own beside an attention layer.  The order list also runs one layer twice and lets
+a run read another run's cache."""
+
+import json
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+D_MODEL, HEADS, KV, HD, FF, VOCAB = 48, 4, 2, 16, 80, 120
+
+
+def make_toy():
+    from socrates_b200.cache import CacheNeeds, StateSpec
+    from socrates_b200.parts import Branch, ParamSpec, Part
+
+    class DecayMixer(Part):
+        """s_t = decay * s_{t-1} + x_t per request; output W s_t.  The state s lives in
+        the request's state slot."""
+        supports_graph = False          # it walks the host-side batch
+
+        def __init__(self, spec, name):
+            super().__init__(spec, name)
+            self.d = spec.params["hidden_size"]
+            self.decay = spec.params["decay"]
+
+        def parameters(self):
+            return {self.name + "proj.weight": ParamSpec((self.d, self.d))}
+
+        def bind(self, tensors, dtype):
+            self.w = tensors[self.name + "proj.weight"]
+
+        def cache_needs(self):
+            return CacheNeeds(state=StateSpec((self.d,), torch.float32))
+
+        def forward(self, ctx, x, cache):
+            state = cache.state()
+            out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+            i = 0
+            for e in ctx.host_batch:
+                s = state[e.row]
+                for _ in e.tokens:
+                    s = self.decay * s + x[i].float()
+                    out[i] = s
+                    i += 1
+                state[e.row] = s
+            return Branch((out @ self.w.float().T).unsqueeze(0).contiguous())
+
+    return DecayMixer
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    decay: float = 0.9
+    architecture = "ToyDecayForCausalLM"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(decay=float(d["decay"]))
+
+    def to_dict(self):
+        return {"architectures": [self.architecture], "decay": self.decay, "vocab_size": VOCAB}
+
+    def plan(self):
+        from socrates_b200.config import LayerSpec, ModelPlan, PartSpec, RunEntry
+        norm = {"dim": D_MODEL, "eps": 1e-5}
+        norms = (PartSpec("rmsnorm", norm, "n1."), PartSpec("rmsnorm", norm, "n2."))
+        ff = PartSpec("swiglu", {"hidden_size": D_MODEL, "intermediate_size": FF}, "mlp.")
+        attn = PartSpec("gqa_attention", {
+            "hidden_size": D_MODEL, "num_heads": HEADS, "num_kv_heads": KV, "head_dim": HD,
+            "scale": HD ** -0.5, "qk_norm_eps": 1e-5, "window": None,
+            "position": PartSpec("rotary", {"head_dim": HD, "rotary_dim": HD, "theta": 1e4})}, "attn.")
+        toy = PartSpec("toy_decay", {"hidden_size": D_MODEL, "decay": self.decay}, "mix.")
+        layers = (LayerSpec("pre_norm", "layers.0.", norms, toy, ff),
+                  LayerSpec("pre_norm", "layers.1.", norms, attn, ff))
+        # layer 0 (state), layer 1 (attention), layer 1 again with a cache of its own,
+        # layer 1 once more reading the cache of its first run, then layer 0 again.
+        order = (RunEntry(0), RunEntry(1), RunEntry(1), RunEntry(1, reads_cache_of=1), RunEntry(0))
+        return ModelPlan(self.architecture, D_MODEL, VOCAB,
+                         PartSpec("embedding", {"vocab_size": VOCAB, "hidden_size": D_MODEL}, "embed."),
+                         layers, order, PartSpec("rmsnorm", norm, "norm."),
+                         PartSpec("lm_head", {"hidden_size": D_MODEL, "vocab_size": VOCAB, "tied_to": None}, "head."))
+
+
+def plain_toy(w, ids, decay):
+    """Whole-sequence statement of the toy model with the plain implementation's functions."""
+    w = {k: v.double() for k, v in w.items()}
+    cfg = {"num_attention_heads": HEADS, "num_key_value_heads": KV, "head_dim": HD, "rms_norm_eps": 1e-5,
+           "rope_theta": 1e4}
+    T = len(ids)
+    pos = torch.arange(T)
+    x = w["embed.weight"][torch.tensor(ids)]
+
+    def toy_layer(x):
+        h = plain.rms_norm(x, w["layers.0.n1.weight"], 1e-5)
+        s, outs = torch.zeros(D_MODEL, dtype=torch.float64), []
+        for t in range(T):
+            s = decay * s + h[t]
+            outs.append(s)
+        x = x + torch.stack(outs) @ w["layers.0.mix.proj.weight"].T
+        return x + plain.swiglu(plain.rms_norm(x, w["layers.0.n2.weight"], 1e-5), w, "layers.0.mlp.")
+
+    def attn_layer(x, kv_from=None):
+        h = plain.rms_norm(x, w["layers.1.n1.weight"], 1e-5)
+        p = "layers.1.attn."
+        q = (h @ w[p + "q_proj.weight"].T).view(T, HEADS, HD)
+        src = h if kv_from is None else kv_from
+        k = (src @ w[p + "k_proj.weight"].T).view(T, KV, HD)
+        v = (src @ w[p + "v_proj.weight"].T).view(T, KV, HD)
+        cos, sin = plain.rope_tables(pos, HD, 1e4)
+        q = plain.apply_rope(plain.rms_norm(q, w[p + "q_norm.weight"], 1e-5), cos, sin)
+        k = plain.apply_rope(plain.rms_norm(k, w[p + "k_norm.weight"], 1e-5), cos, sin)
+        o = plain.attention_core(q, k, v, HD ** -0.5, plain.attention_mask(pos, pos, None))
+        x = x + o.reshape(T, HEADS * HD) @ w[p + "o_proj.weight"].T
+        return x + plain.swiglu(plain.rms_norm(x, w["layers.1.n2.weight"], 1e-5), w, "layers.1.mlp."), h
+
+    x = toy_layer(x)
+    x, h_first = attn_layer(x)
+    x, _ = attn_layer(x)
+    x, _ = attn_layer(x, kv_from=h_first)          # reads the keys and values of the first attention run
+    x = toy_layer(x)
+    return plain.rms_norm(x, w["norm.weight"], 1e-5) @ w["head.weight"].T
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 3e-2)])
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path, dtype, tol):
+    from safetensors.torch import load_file
+    from socrates_b200.cache import CacheManager
+    from socrates_b200.config import register_architecture, unregister_architecture
+    from socrates_b200.engine.engine import build_model
+    from socrates_b200.engine.runner import ModelRunner, StepEntry
+    from socrates_b200.parts import register_part, unregister_part
+    from socrates_b200.weights import write_model_folder
+
+    register_part("mixer", "toy_decay", make_toy())
+    register_architecture(ToyConfig.architecture, ToyConfig)
+    try:
+        folder = write_model_folder(ToyConfig(0.9), seed=4, out_dir=tmp_path / "toy")
+        assert json.loads((folder / "config.json").read_text())["architectures"] == [ToyConfig.architecture]
+        w = load_file(str(folder / "model.safetensors"))
+        config, model = build_model(folder, dtype, DEV)
+        assert isinstance(config, ToyConfig) and not model.supports_graph
+        needs = model.cache_needs()
+        assert needs[0].state is not None and needs[0].paged is None and needs[3] is None
+        cache = CacheManager(needs, 3, 128, 16, 12, dtype, DEV)
+        assert len(cache.groups) == 1 and cache.groups[0].entries == [1, 2] and set(cache.states) == {0, 4}
+        runner = ModelRunner(model, cache, dtype, DEV, max_tokens=128, max_seqs=3)
+
+        g = torch.Generator().manual_seed(0)
+        seqs = [torch.randint(0, VOCAB, (n,), generator=g).tolist() for n in (41, 18)]
+        want = [plain_toy(w, s, 0.9) for s in seqs]
+        got = [[], []]
+        fed = [0, 0]
+        for r in (0, 1):
+            cache.assign(r)
+        # request 0 in portions of 7, 2, 20, then one by one; request 1 joins late, then both decode
+        plan = [[(0, 7)], [(0, 2)], [(0, 20), (1, 5)], [(0, 1), (1, 11)], [(0, 1), (1, 1)], [(0, 1), (1, 1)]]
+        while fed[0] < 41:
+            step = plan.pop(0) if plan else [(0, 1)]
+            entries = []
+            for r, c in step:
+                c = min(c, len(seqs[r]) - fed[r])
+                if c <= 0:
+                    continue
+                assert cache.reserve(r, fed[r] + c)
+                entries.append(StepEntry(r, seqs[r][fed[r]:fed[r] + c], fed[r], list(range(c))))
+            logits = runner.step(entries).logits.double().cpu()
+            i = 0
+            for e in entries:
+                n = len(e.tokens)
+                got[e.row].append(logits[i:i + n])
+                i += n
+                fed[e.row] += n
+                cache.commit(e.row, fed[e.row])
+        for r in (0, 1):
+            mine = torch.cat(got[r])
+            ref = want[r][:mine.shape[0]]
+            assert float((mine - ref).abs().max() / ref.abs().max()) < tol
+        # a new request in a used row starts from a zeroed state
+        cache.release(1)
+        cache.assign(1)
+        assert cache.reserve(1, 4)
+        logits = runner.step([StepEntry(1, seqs[0][:4], 0, [3])]).logits.double().cpu()
+        assert float((logits[0] - want[0][3]).abs().max() / want[0].abs().max()) < tol
+    finally:
+        unregister_part("mixer", "toy_decay")
+        unregister_architecture(ToyConfig.architecture)
