@@ -1,0 +1,299 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Default run: the layer sizes of the Qwen3-4B shape (36 layers, hidden 2560, 32 query
+heads over 8 KV heads, head_dim 128, intermediate 9728, vocabulary 151936, tied head),
+random weights, bfloat16, batch 8, 2,048-token contexts in 8,192-token rows, 16-slot
+pages.  One "step" is one decode step of the whole batch.  It prints ONE JSON line:
+
+  value      decoded tokens a second, K steps timed on the device with CUDA events;
+  e2e        the same through the Python entry point (Engine.step), host tokens in and out;
+  prefill    one 2,048-token prompt in one step: tokens a second and fraction of the
+             bfloat16 tensor peak;
+  roofline   bytes a decode step has to read (every weight once, the live KV) / its time,
+             against the measured copy bandwidth;
+  points     decode tokens a second at batch 1 and 64.
+
+Peaks come from MEASURED_PEAKS.json beside this file when present, else from the
+fallback figures 6.65 TB/s and 1.59 PFLOP/s.
+"""
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN3_4B = {
+    "architectures": ["Qwen3ForCausalLM"], "vocab_size": 151936, "hidden_size": 2560,
+    "intermediate_size": 9728, "num_hidden_layers": 36, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 128, "rms_norm_eps": 1e-6, "rope_theta": 1e6,
+    "tie_word_embeddings": True, "max_position_embeddings": 40960,
+}
+FULL_LAYERS = 36
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            out["hbm_gbs"] = float(d.get("hbm_gbs", out["hbm_gbs"]))
+            out["bf16_tflops"] = float(d.get("bf16_tflops", out["bf16_tflops"]))
+            if "bf16_tflops_sustained" in d:
+                out["bf16_tflops_sustained"] = float(d["bf16_tflops_sustained"])
+            out["source"] = "measured"
+        except Exception:
+            pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.proc, self.lines, self.index = None, [], index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+
+    def summary(self, t0, t1):
+        mhz, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for t, line in self.lines:
+            if not (t0 <= t <= t1 + 0.2):
+                continue
+            f = [x.strip() for x in line.split(",")]
+            try:
+                mhz.append(int(float(f[0])))
+                mx = max(mx, int(float(f[1])))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def arithmetic(cfg, layers):
+    """Bytes a decode step reads and flops a prefill does (analysis/arithmetic.py:84-143
+    of the reference states the same formulas)."""
+    d, F, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    Hq, Hkv, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    linear = layers * ((Hq + 2 * Hkv) * D * d + Hq * D * d + 3 * d * F)
+    kv_per_token = layers * 2 * Hkv * D * 2
+
+    def decode_bytes(batch, ctx):
+        return 2 * (linear + V * d) + batch * ctx * kv_per_token
+
+    def prefill_flops(T):
+        return 2 * T * linear + layers * 2 * Hq * D * T * T + 2 * d * V
+
+    return decode_bytes, prefill_flops
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS,
+                    help="fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-prefill", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+    if args.gpus != 1:
+        print("bench.py: this engine runs on one GPU; --gpus must be 1")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+
+    from socrates_b200 import Engine
+    from socrates_b200.config import config_from_dict
+    from socrates_b200.engine.engine import build_random_model
+    from socrates_b200.engine.runner import SamplingArgs, StepEntry
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    cfg_dict = dict(QWEN3_4B, num_hidden_layers=args.layers)
+    config = config_from_dict(cfg_dict)
+    pk = peaks()
+    decode_bytes, prefill_flops = arithmetic(cfg_dict, args.layers)
+    V = cfg_dict["vocab_size"]
+    gen = torch.Generator().manual_seed(0)
+    K, W, B, ctx = args.steps, args.warmup, args.batch, args.context
+    max_len, page = 8192, 16
+
+    model = build_random_model(config, 0, torch.bfloat16, dev)
+    rows_needed = max(B, 1 if args.skip_points else 64)
+    pages_per_row = -(-(ctx + 2 * (K + W) + 64) // page)
+    engine = Engine(model, device="cuda:0", dtype="bfloat16", compile=True, max_batch=rows_needed,
+                    max_len=max_len, max_new_tokens=K + W + 8, block_size=page,
+                    num_blocks=rows_needed * pages_per_row + 8, token_budget=max(2048, rows_needed))
+    cache, runner = engine.cache, engine.runner
+    for g in cache.groups:                      # live KV: any finite values, the bytes are what is timed
+        g.k.normal_(0, 1, generator=None)
+        g.v.normal_(0, 1, generator=None)
+
+    def decode_run(batch, steps, warmup, sampler=None):
+        """`steps` decode steps of `batch` rows at `ctx` tokens; returns (ms per step, clocks)."""
+        for r in range(batch):
+            cache.assign(r)
+            assert cache.reserve(r, ctx + steps + warmup + 1)
+            cache.commit(r, ctx)
+        ids = torch.randint(0, V, (steps + warmup, batch), generator=gen).tolist()
+        sampling = [SamplingArgs() for _ in range(batch)]
+
+        def one(i):
+            entries = [StepEntry(r, [ids[i][r]], cache.lengths[r], [0]) for r in range(batch)]
+            runner.step(entries, sampling)
+            for r in range(batch):
+                cache.commit(r, cache.lengths[r] + 1)
+
+        for i in range(warmup):
+            one(i)
+        torch.cuda.synchronize()
+        before = runner.kernel_launches
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        start.record()
+        for i in range(warmup, warmup + steps):
+            one(i)
+        end.record()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        ms = start.elapsed_time(end) / steps
+        launches = runner.kernel_launches - before
+        for r in range(batch):
+            cache.release(r)
+        return ms, launches, (t0, t1)
+
+    sampler = ClockSampler()
+    sampler.start()
+    time.sleep(0.3)
+    ms, launches, span = decode_run(B, K, W)
+    clocks = sampler.summary(*span)
+    value = B * 1000.0 / ms
+    need = decode_bytes(B, ctx)
+    achieved = need / (ms * 1e-3) / 1e9
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            pms, _, _ = decode_run(b, max(8, K // 2), W)
+            points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
+
+    prefill = None
+    if not args.skip_prefill:
+        T = 2048
+        prompt = torch.randint(0, V, (T,), generator=gen).tolist()
+        times = []
+        for i in range(W + 3):
+            cache.assign(0)
+            assert cache.reserve(0, T)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            s.record()
+            runner.step([StepEntry(0, prompt, 0, [T - 1])], [SamplingArgs()])
+            e.record()
+            torch.cuda.synchronize()
+            cache.release(0)
+            if i >= W:
+                times.append(s.elapsed_time(e))
+        pms = sorted(times)[len(times) // 2]
+        prefill = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
+                   "frac": round(prefill_flops(T) / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    e2e = None
+    if not args.skip_e2e:
+        # Through the entry point: B requests with ctx-token prompts are prefilled by the
+        # scheduler, then K decode steps are timed; each step copies its inputs from pinned
+        # host memory and reads its sampled tokens back to the host.
+        prompts = torch.randint(1, V, (B, ctx), generator=gen).tolist()
+        reqs = [engine.submit(p, max_new_tokens=K + W + 4) for p in prompts]
+        while any(r.cached < ctx for r in reqs):
+            engine.step()
+        for _ in range(W):
+            engine.step()
+        torch.cuda.synchronize()
+        done_before = sum(len(r.output) for r in reqs)
+        t0 = time.perf_counter()
+        for _ in range(K):
+            engine.step()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        made = sum(len(r.output) for r in reqs) - done_before
+        for r in reqs:
+            r.cancelled = True
+        engine.scheduler.sweep()
+        e2e = {"value": round(made / dt, 1), "unit": "tokens/s",
+               "h2d_bytes_per_step": runner.layout.total * 4, "d2h_bytes_per_step": B * 4}
+    sampler.stop()
+
+    line = {
+        "metric": "decode tokens/s (Qwen3-4B shape, batch 8, 2048-token contexts)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), token ids uniform over the vocabulary",
+        "config": {"model": "Qwen3-4B shape", "layers": args.layers, "layers_full": FULL_LAYERS,
+                   "hidden": 2560, "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 9728,
+                   "vocab": V, "tied_head": True, "global_batch": B, "seq_len": ctx, "max_len": max_len,
+                   "page_size": page, "parallelism": "single GPU", "cuda_graph": True,
+                   "l2": "inputs larger than L2 (weights 8 GB per step)", "peaks": pk["source"]},
+        "clocks": clocks, "gpu_launches": launches, "impl": "ours",
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+    }
+    if prefill is not None:
+        line["prefill"] = prefill
+    if e2e is not None:
+        line["e2e"] = e2e
+    if points:
+        line["points"] = points
+    print(json.dumps(line))
+    return 0
+
+
+REFERENCE_UNAVAILABLE = ("pip install of the reference fails offline: its build backend hatchling is not in "
+                         "/opt/wheelhouse (ModuleNotFoundError: No module named 'hatchling')")
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -129,3 +129,8 @@ def build_library(name: str, sources: Iterable[str], defines: Optional[dict] = N
 
 def build_core() -> Path:
     return build_library("socrates_b200", CORE_SOURCES, libs=("cuda",))
+
+
+def build_all() -> list:
+    """Every library of the package (what `__graft_entry__.build()` compiles)."""
+    return [build_core()]
