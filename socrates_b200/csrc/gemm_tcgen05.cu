@@ -1,0 +1,422 @@
+// C[M,N] = A[M,K] * W[N,K]^T in bfloat16 on the 5th-generation tensor cores:
+// tcgen05.mma with the accumulator in tensor memory, operands brought to shared
+// memory by TMA (128-byte swizzle, K-major), a ring of stages between one producer
+// thread and one MMA thread, and a tcgen05.ld epilogue by four warps.
+//
+// One kernel serves both regimes of the engine:
+//   * many rows (prompt portions): the activations fill the 128 accumulator lanes and
+//     the weights are the N operand (tile 128 x BN, BN up to 256);
+//   * few rows (decode, M <= 64): operands are swapped so that 128 rows of the WEIGHT
+//     matrix fill the lanes and the batch is the N operand (BN = 16, 32 or 64).  The
+//     kernel is then a weight stream at HBM rate; K is cut into `splits` parts so that
+//     narrow matrices still cover every SM, and part z writes float32 partial sums to
+//     C + z*M*N, which the consuming kernel adds up in a fixed order.
+//
+// No cluster launch and no multicast: every block loads its own tiles.  Every wait on
+// an mbarrier is bounded; if one gives up, the block records a code in *status, waits
+// (again bounded) for its own copies in flight, frees its tensor memory and returns.
+#include <cuda.h>
+#include <stdint.h>
+#include <string.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;          // accumulator lanes
+constexpr int BK = 64;           // K elements per stage: one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // a wait gives up after two seconds
+
+// ----------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: false if the phase did not complete within WAIT_LIMIT_NS.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int i = 0; i < 4096; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    for (;;) {
+        for (int i = 0; i < 1024; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > WAIT_LIMIT_NS) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of
+// 128 bytes, 8-row groups 1024 bytes apart (stride byte offset 64 in 16-byte units),
+// leading byte offset 1 (unused with swizzle), descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
+    const uint32_t lo = ((addr & 0x3FFFFu) >> 4) | (1u << 16);
+    const uint32_t hi = 64u | (1u << 14) | (2u << 29);
+    return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = BN.
+__host__ __device__ constexpr uint32_t make_idesc(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(bn >> 3) << 17) |
+           (static_cast<uint32_t>(BM >> 4) << 24);
+}
+
+template <int BN> constexpr int tmem_cols() { return BN < 32 ? 32 : BN; }
+template <int BN> constexpr int stage_bytes() { return BM * BK * 2 + BN * BK * 2; }
+
+template <typename TC> __device__ __forceinline__ void store_out(TC* p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) {
+    *p = __float2bfloat16_rn(v);
+}
+
+// ----------------------------------------------------------------------------- the kernel
+// tma_a: the operand whose rows become accumulator lanes, [rows_a, K], box {64, 128}.
+// tma_b: the operand whose rows become accumulator columns, [rows_b, K], box {64, BN}.
+// SWAP = false: lanes are rows of C (m), columns are columns of C (n).
+// SWAP = true : lanes are columns of C (n), columns are rows of C (m).
+template <int BN, int STAGES, bool SWAP, typename TC>
+__global__ void __launch_bounds__(128)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    TC* __restrict__ C, int M, int N, int K, int kb_per_split, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[STAGES];
+    __shared__ __align__(8) uint64_t accum_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int a0 = blockIdx.x * BM, b0 = blockIdx.y * BN;
+    const int kb_total = (K + BK - 1) / BK;
+    const int kb_begin = blockIdx.z * kb_per_split;
+    const int kb_end = min(kb_total, kb_begin + kb_per_split);
+    const int kb_count = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        mbar_init(smem_u32(&accum_bar), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(tmem_cols<BN>()) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_d = tmem_base_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- producer: TMA loads into the ring
+        int issued = 0;
+        for (int i = 0; i < kb_count; ++i) {
+            const int s = i % STAGES;
+            if (i >= STAGES && !mbar_wait(smem_u32(&empty_bar[s]), ((i / STAGES) - 1) & 1)) {
+                atomicExch(status, 1);
+                atomicExch(&abort_flag, 1);
+                break;
+            }
+            if (*((volatile int*)&abort_flag)) break;
+            const uint32_t bar = smem_u32(&full_bar[s]);
+            const uint32_t sa = tiles + s * stage_bytes<BN>();
+            const uint32_t sb = sa + BM * BK * 2;
+            mbar_arrive_expect_tx(bar, stage_bytes<BN>());
+            tma_load_2d(sa, &tma_a, bar, (kb_begin + i) * BK, a0);
+            tma_load_2d(sb, &tma_b, bar, (kb_begin + i) * BK, b0);
+            issued = i + 1;
+        }
+        if (*((volatile int*)&abort_flag)) {
+            // Wait (bounded) for the copies this thread issued, so none lands after exit.
+            for (int i = max(0, issued - STAGES); i < issued; ++i)
+                mbar_wait(smem_u32(&full_bar[i % STAGES]), (i / STAGES) & 1);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer
+        constexpr uint32_t idesc = make_idesc(BN);
+        bool ok = true;
+        for (int i = 0; i < kb_count && ok; ++i) {
+            const int s = i % STAGES;
+            if (!mbar_wait(smem_u32(&full_bar[s]), (i / STAGES) & 1)) {
+                atomicExch(status, 2);
+                atomicExch(&abort_flag, 1);
+                ok = false;
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t sa = tiles + s * stage_bytes<BN>();
+            const uint32_t sb = sa + BM * BK * 2;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+                const uint64_t da = make_smem_desc(sa + k * UMMA_K * 2);
+                const uint64_t db = make_smem_desc(sb + k * UMMA_K * 2);
+                tcgen05_mma_bf16(tmem_d, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            }
+            tcgen05_commit(smem_u32(&empty_bar[s]));   // frees the stage when these MMAs have read it
+        }
+        tcgen05_commit(smem_u32(&accum_bar));          // arrives when every MMA above has completed
+    }
+    __syncwarp();
+
+    // ---------------- epilogue: all four warps, warp w owns lanes 32w .. 32w+31
+    bool good = mbar_wait(smem_u32(&accum_bar), 0);
+    if (!good) atomicExch(status, 3);
+    if (*((volatile int*)&abort_flag)) good = false;
+    good = __all_sync(0xffffffffu, good);      // tcgen05.ld below needs the whole warp
+    tcgen05_fence_after();
+    if (good && kb_count > 0) {
+        TC* Cz = C + (size_t)blockIdx.z * M * N;
+        const int lane_row = warp * 32 + lane;
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+            uint32_t r[16];
+            tmem_ld16(tmem_d + (static_cast<uint32_t>(warp * 32) << 16) + c0, r);
+            tmem_ld_wait();
+            if (SWAP) {
+                const int n = a0 + lane_row;
+                if (n < N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int m = b0 + c0 + j;
+                        if (m < M) store_out<TC>(Cz + (size_t)m * N + n, __uint_as_float(r[j]));
+                    }
+                }
+            } else {
+                const int m = a0 + lane_row;
+                if (m < M) {
+                    TC* row = Cz + (size_t)m * N + b0 + c0;
+                    if (b0 + c0 + 16 <= N && ((reinterpret_cast<uintptr_t>(row) & 15) == 0)) {
+                        if constexpr (sizeof(TC) == 2) {
+                            uint32_t packed[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]),
+                                                                         __uint_as_float(r[2 * j + 1]));
+                                packed[j] = *reinterpret_cast<uint32_t*>(&v);
+                            }
+                            uint4* dst = reinterpret_cast<uint4*>(row);
+                            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        } else {
+                            uint4* dst = reinterpret_cast<uint4*>(row);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                dst[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (b0 + c0 + j < N) store_out<TC>(row + j, __uint_as_float(r[j]));
+                    }
+                }
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols<BN>())
+                     : "memory");
+    }
+}
+
+// ----------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    int rows, cols, box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = reinterpret_cast<size_t>(k.ptr);
+        h ^= (size_t)k.rows * 0x9E3779B97F4A7C15ull + (size_t)k.cols * 0xC2B2AE3D27D4EB4Full + k.box_rows;
+        return h;
+    }
+};
+
+// Tensor map of a row-major bfloat16 matrix [rows, cols] with boxes of {64 cols, box_rows}
+// and 128-byte swizzle.  Maps are pure functions of their arguments, so they are cached.
+bool get_map(CUtensorMap* out, const void* ptr, int rows, int cols, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, cols, box_rows};
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { *out = it->second; return true; }
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache.size() > 8192) cache.clear();
+    cache[key] = *out;
+    return true;
+}
+
+template <int BN, int STAGES, bool SWAP, typename TC>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, int K, dim3 grid, int kb_per_split,
+           int* status, cudaStream_t stream) {
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, SWAP, TC>;
+    constexpr int smem = STAGES * stage_bytes<BN>() + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) { sb_set_error("gemm_tcgen05: %s", cudaGetErrorString(e)); return (int)e; }
+        configured = true;
+    }
+    kernel<<<grid, 128, smem, stream>>>(ma, mb, (TC*)C, M, N, K, kb_per_split, status);
+    return 0;
+}
+
+template <typename TC>
+int dispatch(const void* A, const void* W, void* C, int M, int N, int K, int splits, int* status,
+             cudaStream_t stream, int* splits_out) {
+    const int kb_total = (K + BK - 1) / BK;
+    if (splits > kb_total) splits = kb_total;
+    const int kb_per_split = (kb_total + splits - 1) / splits;
+    splits = (kb_total + kb_per_split - 1) / kb_per_split;      // no empty part
+    *splits_out = splits;
+    CUtensorMap ma, mb;
+    if (M <= 64) {
+        const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+        if (!get_map(&ma, W, N, K, BM) || !get_map(&mb, A, M, K, bn)) {
+            sb_set_error("gemm_tcgen05: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d)", M, N, K);
+            return SB_ERR_ARG;
+        }
+        dim3 grid((N + BM - 1) / BM, 1, splits);
+        if (bn == 16) return launch<16, 6, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
+        if (bn == 32) return launch<32, 5, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
+        return launch<64, 4, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
+    }
+    const int bn = N >= 256 ? 256 : (N > 64 ? 128 : 64);
+    if (!get_map(&ma, A, M, K, BM) || !get_map(&mb, W, N, K, bn)) {
+        sb_set_error("gemm_tcgen05: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d)", M, N, K);
+        return SB_ERR_ARG;
+    }
+    dim3 grid((M + BM - 1) / BM, (N + bn - 1) / bn, splits);
+    if (bn == 256) return launch<256, 4, false, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
+    if (bn == 128) return launch<128, 3, false, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
+    return launch<64, 4, false, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
+}
+
+}  // namespace
+
+// A [M,K] and W [N,K] bfloat16, row-major, 16-byte aligned, K a multiple of 8.
+// C: c_dtype [M,N] when the effective split count is 1, else float32 [splits, M, N].
+// *splits_io: wanted number of K parts in, number actually written out (never more).
+// status: device int the kernel writes a non-zero code to if a bounded wait gave up.
+extern "C" int sb_gemm_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, int c_dtype,
+                               int* splits_io, int* status, cudaStream_t stream) {
+    SB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
+    SB_REQUIRE(K % 8 == 0, "gemm_tcgen05: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
+    SB_REQUIRE((reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(W) & 15) == 0,
+               "gemm_tcgen05: operands must be 16-byte aligned");
+    SB_REQUIRE(status != nullptr && splits_io != nullptr, "gemm_tcgen05: status and splits are required");
+    int splits = *splits_io;
+    SB_REQUIRE(splits >= 1 && splits <= 64, "gemm_tcgen05: splits=%d is outside 1..64", splits);
+    SB_REQUIRE(splits == 1 || c_dtype == SB_F32, "gemm_tcgen05: partial sums of a split product are float32");
+    SB_REQUIRE((M + 127) / 128 <= 65535 && (N + 63) / 64 <= 65535, "gemm_tcgen05: matrix too large");
+    int rc;
+    if (c_dtype == SB_F32)
+        rc = dispatch<float>(A, W, C, M, N, K, splits, status, stream, splits_io);
+    else if (c_dtype == SB_BF16)
+        rc = dispatch<__nv_bfloat16>(A, W, C, M, N, K, splits, status, stream, splits_io);
+    else
+        SB_REQUIRE(false, "gemm_tcgen05: unknown output dtype %d", c_dtype);
+    if (rc != 0) return rc;
+    SB_LAUNCH_CHECK();
+}
+
+// How many K parts sb_gemm_tcgen05 will actually write for a wanted count (host only).
+extern "C" int sb_gemm_tcgen05_splits(int K, int splits) {
+    const int kb_total = (K + BK - 1) / BK;
+    if (splits > kb_total) splits = kb_total;
+    if (splits < 1) splits = 1;
+    const int per = (kb_total + splits - 1) / splits;
+    return (kb_total + per - 1) / per;
+}

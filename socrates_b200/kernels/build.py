@@ -31,7 +31,8 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
                 "-Xcompiler", "-fPIC"]
 
 # Sources of the core library, in link order.
-CORE_SOURCES = ["errors.cu", "elementwise.cu", "sampling.cu", "gemm_simt.cu", "attention_simt.cu"]
+CORE_SOURCES = ["errors.cu", "elementwise.cu", "sampling.cu", "gemm_simt.cu", "attention_simt.cu",
+                "gemm_tcgen05.cu"]
 
 
 class BuildError(RuntimeError):
@@ -121,6 +122,12 @@ def build_library(name: str, sources: Iterable[str], defines: Optional[dict] = N
         _run([nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp), *[str(o) for o in objs],
               *[f"-l{l}" for l in libs]], f"linking {out.name}")
         os.replace(tmp, out)      # atomic: a concurrent builder sees a whole file or none
+        for old in root.glob(f"lib{name}-*.so"):      # earlier builds of other sources
+            if old != out:
+                try:
+                    old.unlink()
+                except OSError:
+                    pass
     finally:
         shutil.rmtree(work, ignore_errors=True)
     _say(f"built {out.name} in {time.time() - t0:.0f}s")
@@ -128,7 +135,7 @@ def build_library(name: str, sources: Iterable[str], defines: Optional[dict] = N
 
 
 def build_core() -> Path:
-    return build_library("socrates_b200", CORE_SOURCES, libs=("cuda",))
+    return build_library("socrates_b200", CORE_SOURCES)
 
 
 def build_all() -> list:

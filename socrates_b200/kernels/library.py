@@ -34,6 +34,8 @@ _SIGNATURES = {
     "sb_sample": [P, P, P, P, P, I, I, P],
     "sb_gemm_simt": [P, P, P, I, I, I, I, I, I, I, P],
     "sb_attention_simt": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P],
+    "sb_gemm_tcgen05": [P, P, P, I, I, I, I, P, P, P],
+    "sb_gemm_tcgen05_splits": [I, I],
 }
 
 

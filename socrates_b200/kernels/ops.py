@@ -199,3 +199,37 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_p
         block_table.shape[1], _ptr(token_rows), _ptr(positions), N, Hq, Hkv, D, BS, int(window),
         float(scale), num_partitions, _code(q.dtype), _stream()), "attention",
         kernels=2 if num_partitions > 1 else 1)
+
+
+def gemm_tcgen05_splits(K: int, splits: int) -> int:
+    """How many K parts `gemm_tcgen05` writes when `splits` are asked for (never more)."""
+    return library().sb_gemm_tcgen05_splits(int(K), int(splits))
+
+
+def gemm_tcgen05(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, status: torch.Tensor,
+                 splits: int = 1) -> int:
+    """out = a @ w.T on the tcgen05 tensor cores; a [M, K] and w [N, K] bfloat16, K % 8 == 0.
+
+    out is bfloat16 or float32 [M, N], or float32 [S, M, N] partial sums where S =
+    gemm_tcgen05_splits(K, splits).  `status` is an int32 device tensor that receives a
+    non-zero code if a bounded wait inside the kernel gave up.  Returns S.
+    """
+    M, K = a.shape
+    N = w.shape[0]
+    _want(a, "a", torch.bfloat16)
+    _want(w, "w", torch.bfloat16, (N, K))
+    _want(status, "status", torch.int32)
+    S = gemm_tcgen05_splits(K, splits)
+    if out.dim() == 2:
+        if S != 1:
+            raise KernelError("a split product needs a float32 [S, M, N] output")
+        _want(out, "out", None, (M, N))
+    else:
+        _want(out, "out", torch.float32, (S, M, N))
+    lib = library()
+    s_io = ctypes.c_int(S)
+    check(lib, lib.sb_gemm_tcgen05(_ptr(out), _ptr(a), _ptr(w), M, N, K, _code(out.dtype),
+                                   ctypes.byref(s_io), _ptr(status), _stream()), "gemm_tcgen05")
+    if s_io.value != S:
+        raise KernelError(f"gemm_tcgen05 wrote {s_io.value} parts where {S} were expected")
+    return S

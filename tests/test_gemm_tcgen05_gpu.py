@@ -1,0 +1,90 @@
+"""The tcgen05 matrix product alone against a float64 product of the same bfloat16
+operands: many rows (activations on the accumulator lanes), few rows (weights on the
+lanes, K cut into parts), ragged sizes that are no multiple of any tile."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from socrates_b200.kernels import ops, require_kernels
+    require_kernels()
+    return ops
+
+
+def operands(M, N, K, seed=0):
+    g = torch.Generator().manual_seed(seed + M * 7 + N * 3 + K)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16).to(DEV)
+    return a, w, a.double() @ w.double().T
+
+
+def close(out, want, K, bf16_out):
+    # float32 accumulation of K products of unit-variance numbers, then one rounding
+    atol = 1e-4 * math.sqrt(K) + (2 ** -8 * float(want.abs().max()) if bf16_out else 0.0)
+    err = float((out.double() - want).abs().max())
+    assert err <= atol, f"max error {err:.4g} > {atol:.4g}"
+
+
+SHAPES = [
+    # few rows: the weights fill the accumulator lanes
+    (1, 384, 64), (8, 2560, 2560), (16, 200, 96), (17, 1000, 160), (33, 128, 256), (64, 6144, 2560),
+    (5, 151936 // 16, 72),
+    # many rows: the activations fill the lanes
+    (65, 384, 96), (128, 64, 64), (300, 2560, 4096), (1000, 96, 160), (257, 6144, 2560), (130, 200, 72),
+]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_tcgen05(ops, M, N, K):
+    a, w, want = operands(M, N, K)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N), float("nan"), dtype=dtype, device=DEV)
+        ops.gemm_tcgen05(out, a, w, status)
+        close(out, want, K, dtype == torch.bfloat16)
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(8, 2560, 4096, 14), (1, 2560, 9728, 14), (64, 384, 160, 3),
+                                          (16, 96, 64, 4), (300, 2560, 4096, 3)])
+def test_gemm_tcgen05_split_k(ops, M, N, K, splits):
+    a, w, want = operands(M, N, K, seed=1)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    S = ops.gemm_tcgen05_splits(K, splits)
+    assert 1 <= S <= splits
+    out = torch.full((S, M, N), float("nan"), dtype=torch.float32, device=DEV)
+    assert ops.gemm_tcgen05(out, a, w, status, splits) == S
+    close(out.sum(0), want, K, False)
+    assert int(status.item()) == 0
+
+
+def test_gemm_tcgen05_one_hot_rows_and_columns(ops):
+    """Operands that are rows of the identity: the product must reproduce the other
+    operand exactly, which shows a transposed, shifted or swizzle-scrambled tile."""
+    for M, N, K in ((8, 256, 128), (200, 384, 192)):
+        w = torch.randn(N, K).to(torch.bfloat16).to(DEV)
+        a = torch.zeros(M, K, dtype=torch.bfloat16, device=DEV)
+        idx = torch.arange(M) * 5 % K
+        a[torch.arange(M), idx] = 1.0
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+        ops.gemm_tcgen05(out, a, w, status)
+        assert torch.equal(out, w.float()[:, idx.to(DEV)].T.contiguous())
+
+
+def test_gemm_tcgen05_refuses(ops):
+    from socrates_b200.kernels import KernelError
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    a = torch.zeros(4, 20, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 20, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(KernelError, match="multiple of 8"):
+        ops.gemm_tcgen05(torch.empty(4, 8, dtype=torch.float32, device=DEV), a, w, status)
+    with pytest.raises(KernelError):
+        ops.gemm_tcgen05(torch.empty(4, 8, device=DEV), a.float(), w, status)
