@@ -1,0 +1,524 @@
+// Paged causal GQA attention in bfloat16 on the tensor cores (mma.sync m16n8k16,
+// float32 accumulation), flash style: keys and values come from the pages in tiles of
+// 64 keys through cp.async into swizzled shared memory, scores never leave registers,
+// softmax is online in float32 with exp2f.
+//
+// Two kernels share the tile code:
+//   * attn_prefill_kernel: one block per (query tile, KV head).  A query tile is up to
+//     64/G consecutive tokens of ONE request with all G query heads of the KV head:
+//     64 accumulator rows, 16 per warp.  Tiles are found on the device from the step's
+//     request offsets, so the launch shape depends only on the token count.  Queries
+//     see the row's pages from the window's start up to their own position, earlier
+//     portions included.
+//   * attn_decode_kernel: one block per (KV head, token, key partition) for steps in
+//     which every request brings one token.  The G query heads are 16 accumulator rows
+//     shared by the four warps; each warp takes a quarter of every key tile and the
+//     warps are merged at the end; partitions are merged by the reduce kernel.
+//
+// Keys outside [lo, hi) are never read from the pool (their shared-memory rows are
+// zero-filled by cp.async and their scores are masked), so whatever a page's previous
+// owner left in a slot cannot reach the result.  Head sizes 16, 32, 64, 128; group
+// sizes that divide 64 (prefill) or are at most 16 (decode); anything else is refused
+// and runs on the SIMT kernel.
+#include <math.h>
+
+#include "attention_reduce.cuh"
+#include "common.cuh"
+
+using namespace sb;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+constexpr int THREADS = 128;
+constexpr int KT = 64;              // keys per tile
+constexpr float LOG2E = 1.4426950408889634f;
+
+// ----------------------------------------------------------------------------- primitives
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Element offset of 16-byte chunk `chunk` of row `row` in a [rows][D] bfloat16 tile
+// whose chunks are XOR-swizzled so that ldmatrix reads eight rows without bank conflicts.
+template <int D> __device__ __forceinline__ int tile_off(int row, int chunk) {
+    constexpr int CH = D / 8;
+    int x;
+    if (CH >= 8) x = row & 7;
+    else if (CH == 4) x = (row >> 1) & 3;
+    else x = (row >> 2) & 1;
+    return row * D + ((chunk ^ x) << 3);
+}
+
+// Bring keys [tile_start, tile_start + 64) of one KV head into shared memory.  Rows of
+// keys outside [lo, hi) are zero-filled and never read from the pool.
+template <int D>
+__device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const bf16* __restrict__ k_pool,
+                                             const bf16* __restrict__ v_pool, const int* __restrict__ table,
+                                             int BS, int Hkv, int kh, int tile_start, int lo, int hi) {
+    constexpr int CH = D / 8;
+    for (int idx = threadIdx.x; idx < KT * CH; idx += THREADS) {
+        const int key = idx / CH, c = idx - key * CH;
+        const int pos = tile_start + key;
+        const bool valid = pos >= lo && pos < hi;
+        size_t src = 0;
+        if (valid) {
+            const int page = table[pos / BS];
+            src = (((size_t)page * Hkv + kh) * BS + (pos % BS)) * D + c * 8;
+        }
+        const int off = tile_off<D>(key, c);
+        cp_async16(smem_u32(ks + off), k_pool + src, valid ? 16 : 0);
+        cp_async16(smem_u32(vs + off), v_pool + src, valid ? 16 : 0);
+    }
+}
+
+// State of the two accumulator rows a thread owns (rows lane/4 and lane/4 + 8 of the
+// warp's 16): running maximum (raw scores), this thread's share of the running sum, and
+// the output accumulators.
+template <int D> struct RowState {
+    float m[2], l[2];
+    float o[D / 8][4];
+    __device__ __forceinline__ void init() {
+        m[0] = m[1] = -INFINITY;
+        l[0] = l[1] = 0.f;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    }
+};
+
+// One warp: scores of its 16 rows against NK keys of the tile starting at key `kb`,
+// masked by per-row [qlo, qpos] and the block's [klo, khi), then online softmax and PV.
+//   qf: Q fragments of the warp's rows, D/16 k-steps.
+template <int D, int NK>
+__device__ __forceinline__ void warp_tile(RowState<D>& st, const uint32_t (&qf)[D / 16][4], const bf16* ks,
+                                          const bf16* vs, int kb, int tile_start, const int (&qpos)[2],
+                                          const int (&qlo)[2], int klo, int khi, float scale_log2) {
+    const int lane = threadIdx.x & 31;
+    float s[NK / 8][4];
+#pragma unroll
+    for (int i = 0; i < NK / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+
+    // ---- S = Q K^T
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+        for (int nb2 = 0; nb2 < NK / 16; ++nb2) {
+            const int j = lane >> 3;
+            const int key = kb + nb2 * 16 + (j >> 1) * 8 + (lane & 7);
+            uint32_t r[4];
+            ldmatrix_x4(r, smem_u32(ks + tile_off<D>(key, kk * 2 + (j & 1))));
+            mma_bf16(s[2 * nb2], qf[kk], r[0], r[1]);
+            mma_bf16(s[2 * nb2 + 1], qf[kk], r[2], r[3]);
+        }
+    }
+    // ---- mask and row maxima
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nb = 0; nb < NK / 8; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int kpos = tile_start + kb + nb * 8 + 2 * (lane & 3) + (e & 1);
+            const int r = e >> 1;
+            const bool keep = kpos <= qpos[r] && kpos >= qlo[r] && kpos >= klo && kpos < khi;
+            s[nb][e] = keep ? s[nb][e] : -INFINITY;
+            mx[r] = fmaxf(mx[r], s[nb][e]);
+        }
+    }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(st.m[r], mx[r]);
+        m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+        alpha[r] = exp2f((st.m[r] - m_use[r]) * scale_log2);      // m == -inf gives 0
+        st.m[r] = m_new;
+        st.l[r] *= alpha[r];
+    }
+    // ---- P = exp2(S - m) in float32.  For the product with V each weight is split into
+    // two bfloat16 terms, p = hi + lo (16 bits of mantissa together), so that the
+    // softmax weights are not cut to 8 bits before they are used.
+    uint32_t pk_hi[NK / 8][2], pk_lo[NK / 8][2];
+#pragma unroll
+    for (int nb = 0; nb < NK / 8; ++nb) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const float p0 = exp2f((s[nb][2 * r] - m_use[r]) * scale_log2);      // masked: exp2(-inf) = 0
+            const float p1 = exp2f((s[nb][2 * r + 1] - m_use[r]) * scale_log2);
+            st.l[r] += p0 + p1;
+            const uint32_t hi = pack_bf16(p0, p1);
+            pk_hi[nb][r] = hi;
+            pk_lo[nb][r] = pack_bf16(p0 - __uint_as_float(hi << 16), p1 - __uint_as_float(hi & 0xffff0000u));
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+        st.o[i][0] *= alpha[0];
+        st.o[i][1] *= alpha[0];
+        st.o[i][2] *= alpha[1];
+        st.o[i][3] *= alpha[1];
+    }
+    // ---- O += P V
+#pragma unroll
+    for (int k16 = 0; k16 < NK / 16; ++k16) {
+        const uint32_t pa[4] = {pk_hi[2 * k16][0], pk_hi[2 * k16][1], pk_hi[2 * k16 + 1][0], pk_hi[2 * k16 + 1][1]};
+        const uint32_t pb[4] = {pk_lo[2 * k16][0], pk_lo[2 * k16][1], pk_lo[2 * k16 + 1][0], pk_lo[2 * k16 + 1][1]};
+#pragma unroll
+        for (int nb2 = 0; nb2 < D / 16; ++nb2) {
+            const int j = lane >> 3;
+            const int key = kb + k16 * 16 + (j & 1) * 8 + (lane & 7);
+            uint32_t r[4];
+            ldmatrix_x4_trans(r, smem_u32(vs + tile_off<D>(key, nb2 * 2 + (j >> 1))));
+            mma_bf16(st.o[2 * nb2], pa, r[0], r[1]);
+            mma_bf16(st.o[2 * nb2 + 1], pa, r[2], r[3]);
+            mma_bf16(st.o[2 * nb2], pb, r[0], r[1]);
+            mma_bf16(st.o[2 * nb2 + 1], pb, r[2], r[3]);
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------- prefill
+// grid (max_tiles, Hkv).  seq_starts [R+1], seq_rows [R], seq_first_pos [R].
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ k_pool,
+                    const bf16* __restrict__ v_pool, const int* __restrict__ block_table, int table_width,
+                    const int* __restrict__ seq_starts, const int* __restrict__ seq_rows,
+                    const int* __restrict__ seq_first_pos, int R, int Hq, int Hkv, int BS, int window,
+                    float scale_log2) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    bf16* qs = reinterpret_cast<bf16*>(smem);               // [64][D]
+    bf16* kbuf = qs + 64 * D;                               // 2 x [64][D]
+    bf16* vbuf = kbuf + 2 * KT * D;                         // 2 x [64][D]
+
+    const int G = Hq / Hkv;
+    const int TQ = 64 / G;                                  // tokens per tile
+    const int kh = blockIdx.y;
+    // ---- which request, which tile
+    int tile = blockIdx.x, r = 0, t0 = 0, n_tok = 0;
+    for (; r < R; ++r) {
+        const int a = seq_starts[r], len = seq_starts[r + 1] - a;
+        const int tiles = (len + TQ - 1) / TQ;
+        if (tile < tiles) {
+            t0 = a + tile * TQ;
+            n_tok = min(TQ, len - tile * TQ);
+            break;
+        }
+        tile -= tiles;
+    }
+    if (r >= R) return;
+    const int first_pos = seq_first_pos[r] + tile * TQ;
+    const int* table = block_table + (size_t)seq_rows[r] * table_width;
+    const int hi = first_pos + n_tok;                       // keys [lo, hi) are needed by this tile
+    const int lo = (window > 0 && first_pos + 1 > window) ? first_pos + 1 - window : 0;
+    const int tile_begin = lo / KT, tile_end = (hi + KT - 1) / KT;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // ---- Q tile: row = token * G + head
+    constexpr int CH = D / 8;
+    for (int idx = threadIdx.x; idx < 64 * CH; idx += THREADS) {
+        const int row = idx / CH, c = idx - row * CH;
+        const int tok = row / G, g = row - tok * G;
+        const bool valid = tok < n_tok;
+        const bf16* src = q + ((size_t)(t0 + (valid ? tok : 0)) * Hq + kh * G + g) * D + c * 8;
+        cp_async16(smem_u32(qs + tile_off<D>(row, c)), src, valid ? 16 : 0);
+    }
+    load_kv_tile<D>(kbuf, vbuf, k_pool, v_pool, table, BS, Hkv, kh, tile_begin * KT, lo, hi);
+    cp_async_commit();
+
+    int qpos[2], qlo[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int row = warp * 16 + (lane >> 2) + i * 8;
+        const int tok = row / G;
+        qpos[i] = tok < n_tok ? first_pos + tok : -1;       // rows past the tile see no key
+        qlo[i] = (window > 0 && qpos[i] + 1 > window) ? qpos[i] + 1 - window : 0;
+    }
+    RowState<D> st;
+    st.init();
+    uint32_t qf[D / 16][4];
+
+    const int n_tiles = tile_end - tile_begin;
+    for (int i = 0; i < n_tiles; ++i) {
+        const int buf = i & 1;
+        if (i + 1 < n_tiles) {
+            load_kv_tile<D>(kbuf + (buf ^ 1) * KT * D, vbuf + (buf ^ 1) * KT * D, k_pool, v_pool, table, BS, Hkv,
+                            kh, (tile_begin + i + 1) * KT, lo, hi);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (i == 0) {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk)
+                ldmatrix_x4(qf[kk], smem_u32(qs + tile_off<D>(warp * 16 + (lane & 15), kk * 2 + (lane >> 4))));
+        }
+        warp_tile<D, KT>(st, qf, kbuf + buf * KT * D, vbuf + buf * KT * D, 0, (tile_begin + i) * KT, qpos, qlo, lo,
+                         hi, scale_log2);
+        __syncthreads();
+    }
+    // ---- write
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float l = st.l[i];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const int row = warp * 16 + (lane >> 2) + i * 8;
+        const int tok = row / G, g = row - tok * G;
+        if (tok >= n_tok) continue;
+        const float inv = 1.0f / l;
+        bf16* dst = out + ((size_t)(t0 + tok) * Hq + kh * G + g) * D + 2 * (lane & 3);
+#pragma unroll
+        for (int nb = 0; nb < D / 8; ++nb)
+            *reinterpret_cast<uint32_t*>(dst + nb * 8) = pack_bf16(st.o[nb][2 * i] * inv, st.o[nb][2 * i + 1] * inv);
+    }
+}
+
+// ----------------------------------------------------------------------------- decode
+// grid (Hkv, N, NP); every token is one query at position positions[n] of row token_rows[n].
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                   const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                   const int* __restrict__ block_table, int table_width, const int* __restrict__ token_rows,
+                   const int* __restrict__ positions, int Hq, int Hkv, int BS, int window, float scale_log2,
+                   int NP) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    bf16* qs = reinterpret_cast<bf16*>(smem);               // [16][D]
+    bf16* kbuf = qs + 16 * D;                               // 2 x [64][D]
+    bf16* vbuf = kbuf + 2 * KT * D;
+    __shared__ float w_m[4][16], w_l[4][16];
+
+    const int G = Hq / Hkv;
+    const int kh = blockIdx.x, n = blockIdx.y, part = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = positions[n];
+    const int* table = block_table + (size_t)token_rows[n] * table_width;
+    const int hi = pos + 1;
+    const int lo = (window > 0 && hi > window) ? hi - window : 0;
+    const int first_pg = lo / BS, last_pg = (hi - 1) / BS;
+    const int ppp = (last_pg - first_pg + 1 + NP - 1) / NP;
+    const int pg_begin = first_pg + part * ppp;
+    const int pg_end = min(pg_begin + ppp, last_pg + 1);
+    const int k_begin = max(lo, pg_begin * BS);
+    const int k_end = min(hi, pg_end * BS);
+    const int h0 = kh * G;
+
+    if (k_begin >= k_end) {                                 // an empty partition (only when NP > 1)
+        if (threadIdx.x < G) {
+            float* ml = part_ml + (((size_t)n * Hq + h0 + threadIdx.x) * NP + part) * 2;
+            ml[0] = -INFINITY;
+            ml[1] = 0.f;
+        }
+        return;
+    }
+    const int tile_begin = k_begin / KT, tile_end = (k_end + KT - 1) / KT;
+    constexpr int CH = D / 8;
+    for (int idx = threadIdx.x; idx < 16 * CH; idx += THREADS) {
+        const int row = idx / CH, c = idx - row * CH;
+        const bool valid = row < G;
+        const bf16* src = q + ((size_t)n * Hq + h0 + (valid ? row : 0)) * D + c * 8;
+        cp_async16(smem_u32(qs + tile_off<D>(row, c)), src, valid ? 16 : 0);
+    }
+    load_kv_tile<D>(kbuf, vbuf, k_pool, v_pool, table, BS, Hkv, kh, tile_begin * KT, k_begin, k_end);
+    cp_async_commit();
+
+    const int qpos[2] = {pos, pos};
+    const int qlo[2] = {lo, lo};
+    RowState<D> st;
+    st.init();
+    uint32_t qf[D / 16][4];
+    const int n_tiles = tile_end - tile_begin;
+    for (int i = 0; i < n_tiles; ++i) {
+        const int buf = i & 1;
+        if (i + 1 < n_tiles) {
+            load_kv_tile<D>(kbuf + (buf ^ 1) * KT * D, vbuf + (buf ^ 1) * KT * D, k_pool, v_pool, table, BS, Hkv,
+                            kh, (tile_begin + i + 1) * KT, k_begin, k_end);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (i == 0) {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk)
+                ldmatrix_x4(qf[kk], smem_u32(qs + tile_off<D>(lane & 15, kk * 2 + (lane >> 4))));
+        }
+        // warp w takes keys 16w .. 16w+15 of the tile
+        warp_tile<D, 16>(st, qf, kbuf + buf * KT * D, vbuf + buf * KT * D, warp * 16, (tile_begin + i) * KT, qpos,
+                         qlo, k_begin, k_end, scale_log2);
+        __syncthreads();
+    }
+    // ---- merge the four warps: each writes its rows' (m, l, O) to shared memory
+    float* wo = reinterpret_cast<float*>(kbuf);             // [4][16][D] floats: fits in the K and V buffers
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float l = st.l[i];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const int row = (lane >> 2) + i * 8;
+        if ((lane & 3) == 0) { w_m[warp][row] = st.m[i]; w_l[warp][row] = l; }
+#pragma unroll
+        for (int nb = 0; nb < D / 8; ++nb) {
+            float* dst = wo + ((size_t)(warp * 16 + row)) * D + nb * 8 + 2 * (lane & 3);
+            dst[0] = st.o[nb][2 * i];
+            dst[1] = st.o[nb][2 * i + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += THREADS) {
+        const int row = idx / D, d = idx - row * D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+            if (w_l[w][row] > 0.f) M = fmaxf(M, w_m[w][row]);
+        float L = 0.f, o = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            if (w_l[w][row] > 0.f) {
+                const float f = exp2f((w_m[w][row] - M) * scale_log2);
+                L += f * w_l[w][row];
+                o += f * wo[((size_t)(w * 16 + row)) * D + d];
+            }
+        }
+        const int h = h0 + row;
+        if (NP == 1) {
+            out[((size_t)n * Hq + h) * D + d] = __float2bfloat16_rn(o / L);
+        } else {
+            part_o[(((size_t)n * Hq + h) * NP + part) * D + d] = o;
+            if (d == 0) {
+                float* ml = part_ml + (((size_t)n * Hq + h) * NP + part) * 2;
+                ml[0] = M * scale_log2 / LOG2E;             // the reduce kernel works with natural exponents
+                ml[1] = L;
+            }
+        }
+    }
+}
+
+template <int D> constexpr int prefill_smem() { return (64 * D + 4 * KT * D) * 2; }
+template <int D> constexpr int decode_smem() { return (16 * D + 4 * KT * D) * 2; }
+
+template <int D>
+int launch_prefill(void* out, const void* q, const void* k_pool, const void* v_pool, const int* block_table,
+                   int table_width, const int* seq_starts, const int* seq_rows, const int* seq_first_pos, int R,
+                   int N, int Hq, int Hkv, int BS, int window, float scale, cudaStream_t stream) {
+    auto kernel = attn_prefill_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, prefill_smem<D>());
+        if (e != cudaSuccess) { sb_set_error("attention_mma: %s", cudaGetErrorString(e)); return (int)e; }
+        configured = true;
+    }
+    const int TQ = 64 / (Hq / Hkv);
+    dim3 grid(N / TQ + R, Hkv);                              // an upper bound of the number of tiles
+    kernel<<<grid, THREADS, prefill_smem<D>(), stream>>>(
+        (bf16*)out, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, table_width, seq_starts,
+        seq_rows, seq_first_pos, R, Hq, Hkv, BS, window, scale * LOG2E);
+    return 0;
+}
+
+template <int D>
+int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool, const void* v_pool,
+                  const int* block_table, int table_width, const int* token_rows, const int* positions, int N,
+                  int Hq, int Hkv, int BS, int window, float scale, int NP, cudaStream_t stream) {
+    auto kernel = attn_decode_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, decode_smem<D>());
+        if (e != cudaSuccess) { sb_set_error("attention_mma: %s", cudaGetErrorString(e)); return (int)e; }
+        configured = true;
+    }
+    dim3 grid(Hkv, N, NP);
+    kernel<<<grid, THREADS, decode_smem<D>(), stream>>>(
+        (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
+        table_width, token_rows, positions, Hq, Hkv, BS, window, scale * LOG2E, NP);
+    if (NP > 1) {
+        dim3 rgrid(Hq, N);
+        attn_reduce_kernel<bf16><<<rgrid, 128, 0, stream>>>((bf16*)out, part_o, part_ml, Hq, D, NP);
+    }
+    return 0;
+}
+
+}  // namespace
+
+// 1 if the tensor-core kernels take this shape (bfloat16 only), else 0.
+extern "C" int sb_attention_mma_supports(int Hq, int Hkv, int D, int page_size, int decode) {
+    if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return 0;
+    if (!(D == 16 || D == 32 || D == 64 || D == 128)) return 0;
+    if (page_size <= 0) return 0;
+    const int G = Hq / Hkv;
+    return decode ? (G <= 16) : (64 % G == 0);
+}
+
+// Prompt portions and mixed steps: requests r = 0..R-1 bring tokens
+// seq_starts[r] .. seq_starts[r+1]-1 at positions seq_first_pos[r]... of cache row seq_rows[r].
+extern "C" int sb_attention_prefill_mma(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                        const int* block_table, int table_width, const int* seq_starts,
+                                        const int* seq_rows, const int* seq_first_pos, int R, int N, int Hq,
+                                        int Hkv, int D, int page_size, int window, float scale,
+                                        cudaStream_t stream) {
+    SB_REQUIRE(sb_attention_mma_supports(Hq, Hkv, D, page_size, 0),
+               "attention_mma (prefill): Hq=%d Hkv=%d head_dim=%d is not supported", Hq, Hkv, D);
+    SB_REQUIRE(R > 0 && N > 0 && window >= 0 && table_width > 0, "attention_mma: bad sizes R=%d N=%d", R, N);
+    int rc;
+    switch (D) {
+        case 16: rc = launch_prefill<16>(out, q, k_pool, v_pool, block_table, table_width, seq_starts, seq_rows, seq_first_pos, R, N, Hq, Hkv, page_size, window, scale, stream); break;
+        case 32: rc = launch_prefill<32>(out, q, k_pool, v_pool, block_table, table_width, seq_starts, seq_rows, seq_first_pos, R, N, Hq, Hkv, page_size, window, scale, stream); break;
+        case 64: rc = launch_prefill<64>(out, q, k_pool, v_pool, block_table, table_width, seq_starts, seq_rows, seq_first_pos, R, N, Hq, Hkv, page_size, window, scale, stream); break;
+        default: rc = launch_prefill<128>(out, q, k_pool, v_pool, block_table, table_width, seq_starts, seq_rows, seq_first_pos, R, N, Hq, Hkv, page_size, window, scale, stream); break;
+    }
+    if (rc != 0) return rc;
+    SB_LAUNCH_CHECK();
+}
+
+// Steps in which every request brings one token.  Scratch as for sb_attention_simt.
+extern "C" int sb_attention_decode_mma(void* out, float* part_o, float* part_ml, const void* q,
+                                       const void* k_pool, const void* v_pool, const int* block_table,
+                                       int table_width, const int* token_rows, const int* positions, int N,
+                                       int Hq, int Hkv, int D, int page_size, int window, float scale,
+                                       int num_partitions, cudaStream_t stream) {
+    SB_REQUIRE(sb_attention_mma_supports(Hq, Hkv, D, page_size, 1),
+               "attention_mma (decode): Hq=%d Hkv=%d head_dim=%d is not supported", Hq, Hkv, D);
+    SB_REQUIRE(N > 0 && N <= 65535 && window >= 0 && table_width > 0, "attention_mma: bad sizes N=%d", N);
+    SB_REQUIRE(num_partitions >= 1 && num_partitions <= 65535, "attention_mma: %d partitions", num_partitions);
+    SB_REQUIRE(num_partitions == 1 || (part_o != nullptr && part_ml != nullptr),
+               "attention_mma: split over %d partitions needs scratch buffers", num_partitions);
+    int rc;
+    switch (D) {
+        case 16: rc = launch_decode<16>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream); break;
+        case 32: rc = launch_decode<32>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream); break;
+        case 64: rc = launch_decode<64>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream); break;
+        default: rc = launch_decode<128>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream); break;
+    }
+    if (rc != 0) return rc;
+    SB_LAUNCH_CHECK();
+}

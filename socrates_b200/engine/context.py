@@ -79,7 +79,8 @@ class CacheView:
 class StepContext:
     def __init__(self, dtype: torch.dtype, device, buffers: Buffers, num_tokens: int, num_seqs: int,
                  token_ids, positions, token_rows, seq_starts, seq_rows, seq_first_pos, logit_index,
-                 all_decode: bool, max_context: int, host_batch=None, num_sms: int = 148):
+                 all_decode: bool, max_context: int, host_batch=None, num_sms: int = 148,
+                 status: Optional[torch.Tensor] = None):
         self.dtype, self.device, self.buffers = dtype, device, buffers
         self.num_tokens, self.num_seqs = num_tokens, num_seqs
         self.token_ids, self.positions, self.token_rows = token_ids, positions, token_rows
@@ -89,31 +90,71 @@ class StepContext:
         self.max_context = max_context      # upper bound of any request's length after this step
         self.host_batch = host_batch        # the host-side entries; None while a graph is recorded
         self.num_sms = num_sms
+        self.status = status                # int32 device word the tensor-core kernels report to
 
     # ------------------------------------------------------------------ kernel choice
+    def uses_tensor_cores(self, x_dtype: torch.dtype, w: torch.Tensor) -> bool:
+        """The tcgen05 kernel takes bfloat16 operands with 16-byte rows; everything else
+        (the float32 engine, a matrix stored in float32, an odd K) runs on the CUDA cores."""
+        return (x_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0
+                and self.status is not None)
+
+    def gemm_splits(self, M: int, w: torch.Tensor, x_dtype: torch.dtype) -> int:
+        """Into how many K parts a product whose output is partial sums is cut.
+
+        Only the weight-streaming regime (M <= 64) is cut: enough blocks to keep two
+        resident on every SM, at least two K blocks of 64 each.  A function of the
+        shapes alone, so a recorded graph stays valid.
+        """
+        if not self.uses_tensor_cores(x_dtype, w) or M > 64:
+            return 1
+        N, K = w.shape
+        tiles = -(-N // 128)
+        want = max(1, (2 * self.num_sms) // tiles)
+        most = max(1, (-(-K // 64)) // 2)
+        return ops.gemm_tcgen05_splits(K, min(want, most, 16))
+
     def gemm(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> None:
         """out = x w^T; out is [M, N] or float32 partial sums [S, M, N]."""
-        ops.gemm_simt(out, x, w, splits=out.shape[0] if out.dim() == 3 else 1)
+        S = out.shape[0] if out.dim() == 3 else 1
+        if self.uses_tensor_cores(x.dtype, w):
+            ops.gemm_tcgen05(out if out.dim() == 3 and S > 1 else out.view(out.shape[-2], out.shape[-1]),
+                             x, w, self.status, S)
+        else:
+            ops.gemm_simt(out, x, w, splits=S)
 
-    def attention_partitions(self, num_kv_heads: int, page_size: int) -> int:
-        """Into how many key partitions the SIMT attention splits each query.
+    def attention_partitions(self, num_kv_heads: int, page_size: int, keys_per_part: int) -> int:
+        """Into how many key partitions each query's keys are cut.
 
         A function of static quantities only (batch width, limits), so that a recorded
-        graph stays valid: enough blocks to fill the SMs twice, never more partitions
-        than the longest row has pages.
+        graph stays valid: enough blocks to fill the SMs twice, never less than
+        `keys_per_part` keys of the longest possible row in a partition.
         """
         blocks = max(1, num_kv_heads * self.num_tokens)
         want = -(-2 * self.num_sms // blocks)
-        most = max(1, -(-self.max_context // (4 * page_size)))
+        most = max(1, -(-self.max_context // keys_per_part))
         return max(1, min(want, most, 64))
 
     def attention(self, out, q, k_pool, v_pool, table, num_heads: int, scale: float, window: int) -> None:
+        """Causal attention of every token of the step over its row's pages.
+
+        bfloat16 with a head size and group size the tensor-core kernels take: the
+        decode kernel when every request brings one token, else the tile kernel;
+        everything else (the float32 engine above all) runs on the SIMT kernel.
+        """
         Hkv, page_size, D = k_pool.shape[1], k_pool.shape[2], k_pool.shape[3]
-        NP = self.attention_partitions(Hkv, page_size)
+        N = q.shape[0]
+        tensor_cores = q.dtype == torch.bfloat16
+        if tensor_cores and not self.all_decode and ops.attention_mma_supports(num_heads, Hkv, D, page_size, False):
+            ops.attention_prefill_mma(out, q, k_pool, v_pool, table, self.seq_starts, self.seq_rows,
+                                      self.seq_first_pos, num_heads, scale, window)
+            return
+        use_mma = tensor_cores and self.all_decode and ops.attention_mma_supports(num_heads, Hkv, D, page_size, True)
+        NP = self.attention_partitions(Hkv, page_size, 256 if use_mma else 4 * page_size)
         part_o = part_ml = None
         if NP > 1:
-            N = q.shape[0]
             part_o = self.buffers.take_flat("attn_part_o", N * num_heads * NP * D, torch.float32)
             part_ml = self.buffers.take_flat("attn_part_ml", N * num_heads * NP * 2, torch.float32)
-        ops.attention_simt(out, q, k_pool, v_pool, table, self.token_rows, self.positions, num_heads,
-                           scale, window, NP, part_o, part_ml)
+        fn = ops.attention_decode_mma if use_mma else ops.attention_simt
+        fn(out, q, k_pool, v_pool, table, self.token_rows, self.positions, num_heads, scale, window, NP,
+           part_o, part_ml)

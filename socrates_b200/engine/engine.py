@@ -130,7 +130,8 @@ class Engine:
                    for e in plan.entries]
         args = [SamplingArgs(t, s, c) for (t, s, c) in self.scheduler.sampling_args(plan)]
         result = self.runner.step(entries, args)
-        tokens = result.tokens.tolist() if result.tokens is not None else []   # the step's one read-back
+        tokens = result.tokens.tolist() if result.tokens is not None else []   # the step's read-back
+        self.runner.check_status()
         self.scheduler.complete(plan, tokens)
         self.steps += 1
         return True

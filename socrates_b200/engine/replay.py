@@ -105,6 +105,7 @@ def main(argv=None) -> int:
                 arr.tofile(str(out_dir / f"{number}.f32"))
             else:
                 torch.cuda.current_stream().synchronize()
+            runner.check_status()
         for rid in step.get("end", []):
             rid = str(rid)
             if rid in rows:

@@ -79,6 +79,7 @@ class ModelRunner:
                          for _ in range(4)]
         self._next = 0
         self.sampled = torch.zeros(max_tokens, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.use_graphs = use_graphs and model.supports_graph
         self._graphs: Dict[Tuple[int, int, bool], Tuple[torch.cuda.CUDAGraph, Optional[torch.Tensor]]] = {}
         self._eager_decode_done: set = set()
@@ -174,7 +175,18 @@ class ModelRunner:
             seq_starts=m[L.seq_starts:L.seq_starts + R + 1], seq_rows=m[L.seq_rows:L.seq_rows + R],
             seq_first_pos=m[L.seq_first:L.seq_first + R],
             logit_index=m[L.logit:L.logit + M] if M else None,
-            all_decode=all_decode, max_context=max_ctx, host_batch=host_batch, num_sms=self.num_sms)
+            all_decode=all_decode, max_context=max_ctx, host_batch=host_batch, num_sms=self.num_sms,
+            status=self.status)
+
+    def check_status(self) -> None:
+        """Raise if a kernel reported that one of its bounded waits gave up.  Reads one
+        word back, so call it where the host synchronises anyway (after a step's tokens
+        or logits were read)."""
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise RuntimeError(f"a tensor-core kernel gave up waiting on its pipeline (code {code}); "
+                               f"the step's results are not valid")
 
     def _run(self, ctx: StepContext, M: int, sample: bool):
         logits = self.model.forward(ctx, self.cache)

@@ -233,3 +233,67 @@ def gemm_tcgen05(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, status: to
     if s_io.value != S:
         raise KernelError(f"gemm_tcgen05 wrote {s_io.value} parts where {S} were expected")
     return S
+
+
+def attention_mma_supports(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                           decode: bool) -> bool:
+    """Whether the tensor-core attention kernels take this shape (bfloat16 only)."""
+    return bool(library().sb_attention_mma_supports(num_heads, num_kv_heads, head_dim, page_size,
+                                                    int(decode)))
+
+
+def attention_prefill_mma(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                          block_table: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor,
+                          seq_first_pos: torch.Tensor, num_heads: int, scale: float, window: int = 0) -> None:
+    """Paged causal attention of prompt portions on the tensor cores (bfloat16).
+
+    Request r brings tokens seq_starts[r] .. seq_starts[r+1]-1 (rows of q and out) at
+    positions seq_first_pos[r], +1, ... of cache row seq_rows[r]; its keys, earlier
+    portions included, are read from the pages.
+    """
+    N = q.shape[0]
+    _, Hkv, BS, D = k_pool.shape
+    R = seq_rows.numel()
+    _want(q, "q", torch.bfloat16, (N, num_heads * D))
+    _want(out, "out", torch.bfloat16, (N, num_heads * D))
+    _want(k_pool, "k_pool", torch.bfloat16)
+    _want(v_pool, "v_pool", torch.bfloat16, k_pool.shape)
+    _want(block_table, "block_table", torch.int32)
+    _want(seq_starts, "seq_starts", torch.int32, (R + 1,))
+    _want(seq_rows, "seq_rows", torch.int32, (R,))
+    _want(seq_first_pos, "seq_first_pos", torch.int32, (R,))
+    lib = library()
+    check(lib, lib.sb_attention_prefill_mma(
+        _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
+        _ptr(seq_starts), _ptr(seq_rows), _ptr(seq_first_pos), R, N, num_heads, Hkv, D, BS, int(window),
+        float(scale), _stream()), "attention_prefill_mma")
+
+
+def attention_decode_mma(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                         block_table: torch.Tensor, token_rows: torch.Tensor, positions: torch.Tensor,
+                         num_heads: int, scale: float, window: int = 0, num_partitions: int = 1,
+                         part_o: Optional[torch.Tensor] = None,
+                         part_ml: Optional[torch.Tensor] = None) -> None:
+    """Paged attention of single decode tokens on the tensor cores (bfloat16), the keys
+    of each token cut into `num_partitions` parts; arguments as `attention_simt`."""
+    N = q.shape[0]
+    _, Hkv, BS, D = k_pool.shape
+    Hq = num_heads
+    _want(q, "q", torch.bfloat16, (N, Hq * D))
+    _want(out, "out", torch.bfloat16, (N, Hq * D))
+    _want(k_pool, "k_pool", torch.bfloat16)
+    _want(v_pool, "v_pool", torch.bfloat16, k_pool.shape)
+    _want(block_table, "block_table", torch.int32)
+    _want(token_rows, "token_rows", torch.int32, (N,))
+    _want(positions, "positions", torch.int32, (N,))
+    if num_partitions > 1:
+        _want(part_o, "part_o", torch.float32)
+        _want(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < N * Hq * num_partitions * D or part_ml.numel() < N * Hq * num_partitions * 2:
+            raise KernelError("attention scratch buffers are too small")
+    lib = library()
+    check(lib, lib.sb_attention_decode_mma(
+        _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+        block_table.shape[1], _ptr(token_rows), _ptr(positions), N, Hq, Hkv, D, BS, int(window),
+        float(scale), num_partitions, _stream()), "attention_decode_mma",
+        kernels=2 if num_partitions > 1 else 1)

@@ -30,7 +30,8 @@ class Linear:
         elif out == "float32":
             y = ctx.buffers.take(buffer, M, (N,), torch.float32)
         elif out == "partial":
-            y = ctx.buffers.take_flat(buffer, M * N, torch.float32).view(1, M, N)
+            S = ctx.gemm_splits(M, self.weight, x.dtype)
+            y = ctx.buffers.take_flat(buffer, S * M * N, torch.float32).view(S, M, N)
         else:
             raise ValueError(out)
         ctx.gemm(y, x, self.weight)
