@@ -522,3 +522,60 @@ extern "C" int sb_attention_decode_mma(void* out, float* part_o, float* part_ml,
     if (rc != 0) return rc;
     SB_LAUNCH_CHECK();
 }
+
+// ----------------------------------------------------------------------------------------
+// The variant that allocates nothing (see no_alloc.h): scratch for the key partitions
+// lives in this file-scope device array.  In host code the name below is only a handle
+// for cudaGetSymbolAddress, never a pointer a kernel may be given.
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[SB_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};   // device address of the array, per device
+}  // namespace
+
+extern "C" int sb_attention_decode_mma_noalloc(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                               const int* block_table, int table_width, const int* token_rows,
+                                               const int* positions, int tokens, int query_heads, int kv_heads,
+                                               int head_dim, int page_size, int window, float scale,
+                                               int num_partitions, cudaStream_t stream) {
+    SB_REQUIRE(sb_attention_mma_supports(query_heads, kv_heads, head_dim, page_size, 1),
+               "attention (no-alloc): Hq=%d Hkv=%d head_dim=%d is not supported", query_heads, kv_heads, head_dim);
+    SB_REQUIRE(tokens > 0 && tokens <= 65535 && window >= 0 && table_width > 0,
+               "attention (no-alloc): bad sizes tokens=%d", tokens);
+    SB_REQUIRE(num_partitions >= 1 && num_partitions <= 65535, "attention (no-alloc): %d partitions",
+               num_partitions);
+    const long long slots = (long long)tokens * query_heads * num_partitions;
+    const long long need = slots * (head_dim + 2);
+    SB_REQUIRE(need <= (long long)SB_NOALLOC_MAX_FLOATS,
+               "attention (no-alloc): tokens*heads*partitions*(head_dim+2) = %lld floats exceed the built-in "
+               "scratch of %d floats; use fewer partitions or the entry point that takes scratch buffers",
+               need, SB_NOALLOC_MAX_FLOATS);
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) { sb_set_error("attention (no-alloc): %s", cudaGetErrorString(e)); return (int)e; }
+    SB_REQUIRE(device >= 0 && device < kMaxDevices, "attention (no-alloc): device %d is not supported", device);
+    if (g_noalloc_ptr[device] == nullptr) {
+        // Once per device, with that device current: the array's address on THIS device.
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            sb_set_error("attention (no-alloc): cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return e != cudaSuccess ? (int)e : SB_ERR_ARG;
+        }
+        g_noalloc_ptr[device] = p;
+    }
+    float* part_o = g_noalloc_ptr[device];                     // [tokens, heads, partitions, head_dim]
+    float* part_ml = part_o + slots * head_dim;                // [tokens, heads, partitions, 2]
+    int rc;
+    switch (head_dim) {
+        case 16: rc = launch_decode<16>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, tokens, query_heads, kv_heads, page_size, window, scale, num_partitions, stream); break;
+        case 32: rc = launch_decode<32>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, tokens, query_heads, kv_heads, page_size, window, scale, num_partitions, stream); break;
+        case 64: rc = launch_decode<64>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, tokens, query_heads, kv_heads, page_size, window, scale, num_partitions, stream); break;
+        default: rc = launch_decode<128>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, tokens, query_heads, kv_heads, page_size, window, scale, num_partitions, stream); break;
+    }
+    if (rc != 0) return rc;
+    SB_LAUNCH_CHECK();
+}
