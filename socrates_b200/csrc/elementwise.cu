@@ -19,16 +19,41 @@ __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ tabl
     for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_float(src[i]);
 }
 
+// d a multiple of 8 (bfloat16) or 4 (float32): 16-byte loads, one thread per vector.
+template <typename T>
+__global__ void embed_vec_kernel(float* __restrict__ out, const T* __restrict__ table,
+                                 const int* __restrict__ ids, int d, int V) {
+    constexpr int VEC = Vec16<T>::N;
+    const int n = blockIdx.x;
+    int id = ids[n];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    const T* src = table + (size_t)id * d;
+    float* dst = out + (size_t)n * d;
+    for (int i = threadIdx.x * VEC; i < d; i += blockDim.x * VEC) {
+        Vec16<T> v;
+        v.load(src + i);
+#pragma unroll
+        for (int e = 0; e < VEC; e += 4)
+            *reinterpret_cast<float4*>(dst + i + e) = make_float4(v.get(e), v.get(e + 1), v.get(e + 2), v.get(e + 3));
+    }
+}
+
 extern "C" int sb_embed(float* out, const void* table, const int* ids, int N, int d, int V,
                         int dtype, cudaStream_t stream) {
     SB_REQUIRE(N >= 0 && d > 0 && V > 0, "embed: bad sizes N=%d d=%d V=%d", N, d, V);
     if (N == 0) return 0;
-    if (dtype == SB_F32)
-        embed_kernel<float><<<N, 256, 0, stream>>>(out, (const float*)table, ids, d, V);
-    else if (dtype == SB_BF16)
-        embed_kernel<__nv_bfloat16><<<N, 256, 0, stream>>>(out, (const __nv_bfloat16*)table, ids, d, V);
-    else
+    const bool aligned = (reinterpret_cast<uintptr_t>(table) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    if (dtype == SB_F32) {
+        if (aligned && d % 4 == 0) embed_vec_kernel<float><<<N, 256, 0, stream>>>(out, (const float*)table, ids, d, V);
+        else embed_kernel<float><<<N, 256, 0, stream>>>(out, (const float*)table, ids, d, V);
+    } else if (dtype == SB_BF16) {
+        if (aligned && d % 8 == 0)
+            embed_vec_kernel<__nv_bfloat16><<<N, 256, 0, stream>>>(out, (const __nv_bfloat16*)table, ids, d, V);
+        else
+            embed_kernel<__nv_bfloat16><<<N, 256, 0, stream>>>(out, (const __nv_bfloat16*)table, ids, d, V);
+    } else {
         SB_REQUIRE(false, "embed: unknown dtype %d", dtype);
+    }
     SB_LAUNCH_CHECK();
 }
 
@@ -64,6 +89,62 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
     for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<T>(row[i] * rinv * gain[i]);
 }
 
+// The same with 16-byte accesses (d a multiple of 4, 16-byte aligned rows): each thread
+// owns whole float4 columns, the S partial sums of a column are loaded back to back
+// (independent loads) and added in the fixed order s = 0, 1, ...
+template <typename T>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ delta,
+                                       int S, size_t delta_stride, const float* __restrict__ gain,
+                                       T* __restrict__ out, const int* __restrict__ row_index, int d,
+                                       float eps, int write_residual) {
+    extern __shared__ float row[];          // d floats
+    __shared__ float scratch[33];
+    const int m = blockIdx.x;
+    const int r = row_index ? row_index[m] : m;
+    float4* res4 = reinterpret_cast<float4*>(residual + (size_t)r * d);
+    const float4* del4 = reinterpret_cast<const float4*>(delta + (size_t)r * d);
+    const size_t stride4 = delta_stride / 4;
+    float4* row4 = reinterpret_cast<float4*>(row);
+    const int d4 = d / 4;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d4; i += blockDim.x) {
+        float4 v = res4[i];
+        int s = 0;
+        for (; s + 4 <= S; s += 4) {
+            const float4 a = __ldg(del4 + (s + 0) * stride4 + i), b = __ldg(del4 + (s + 1) * stride4 + i);
+            const float4 c = __ldg(del4 + (s + 2) * stride4 + i), e = __ldg(del4 + (s + 3) * stride4 + i);
+            v.x = ((((v.x + a.x) + b.x) + c.x) + e.x);
+            v.y = ((((v.y + a.y) + b.y) + c.y) + e.y);
+            v.z = ((((v.z + a.z) + b.z) + c.z) + e.z);
+            v.w = ((((v.w + a.w) + b.w) + c.w) + e.w);
+        }
+        for (; s < S; ++s) {
+            const float4 a = __ldg(del4 + s * stride4 + i);
+            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+        }
+        row4[i] = v;
+        if (write_residual) res4[i] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    const float total = block_sum(ss, scratch);
+    const float rinv = 1.0f / sqrtf(total / (float)d + eps);
+    const float4* gain4 = reinterpret_cast<const float4*>(gain);
+    T* o = out + (size_t)m * d;
+    for (int i = threadIdx.x; i < d4; i += blockDim.x) {
+        const float4 v = row4[i], g = __ldg(gain4 + i);
+        const float a = v.x * rinv * g.x, b = v.y * rinv * g.y, c = v.z * rinv * g.z, e = v.w * rinv * g.w;
+        if constexpr (sizeof(T) == 2) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, e);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(o + 4 * i) = pk;
+        } else {
+            *reinterpret_cast<float4*>(o + 4 * i) = make_float4(a, b, c, e);
+        }
+    }
+}
+
 extern "C" int sb_add_rmsnorm(float* residual, const float* delta, int S, long long delta_stride,
                               const float* gain, void* out, const int* row_index, int M, int d,
                               float eps, int dtype, cudaStream_t stream) {
@@ -73,20 +154,27 @@ extern "C" int sb_add_rmsnorm(float* residual, const float* delta, int S, long l
     const size_t smem = (size_t)d * sizeof(float);
     SB_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: width %d does not fit one block's shared memory", d);
     const int write_residual = row_index == nullptr && S > 0;
-    const int threads = d >= 2048 ? 512 : 256;
+    const bool vec = d % 4 == 0 && delta_stride % 4 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(delta) |
+                       reinterpret_cast<uintptr_t>(gain) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    const int threads = vec ? (d >= 4096 ? 512 : 256) : (d >= 2048 ? 512 : 256);
+#define SB_NORM_LAUNCH(KERNEL, T)                                                                        \
+    do {                                                                                                  \
+        if (smem > 48 * 1024)                                                                             \
+            cudaFuncSetAttribute(KERNEL<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+        KERNEL<T><<<M, threads, smem, stream>>>(residual, delta, S, (size_t)delta_stride, gain, (T*)out,  \
+                                                row_index, d, eps, write_residual);                      \
+    } while (0)
     if (dtype == SB_F32) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<float><<<M, threads, smem, stream>>>(
-            residual, delta, S, (size_t)delta_stride, gain, (float*)out, row_index, d, eps, write_residual);
+        if (vec) SB_NORM_LAUNCH(add_rmsnorm_vec_kernel, float);
+        else SB_NORM_LAUNCH(add_rmsnorm_kernel, float);
     } else if (dtype == SB_BF16) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<__nv_bfloat16><<<M, threads, smem, stream>>>(
-            residual, delta, S, (size_t)delta_stride, gain, (__nv_bfloat16*)out, row_index, d, eps, write_residual);
+        if (vec) SB_NORM_LAUNCH(add_rmsnorm_vec_kernel, __nv_bfloat16);
+        else SB_NORM_LAUNCH(add_rmsnorm_kernel, __nv_bfloat16);
     } else {
         SB_REQUIRE(false, "add_rmsnorm: unknown dtype %d", dtype);
     }
+#undef SB_NORM_LAUNCH
     SB_LAUNCH_CHECK();
 }
 
@@ -98,9 +186,12 @@ extern "C" int sb_add_rmsnorm(float* residual, const float* delta, int S, long l
 // page = block_table[row, pos / BS], off = pos % BS.  A null gain means no norm.
 // Rotation: angle_j = float(pos) * inv_freq[j], j < R/2; dim j pairs with j + R/2;
 // dims >= R pass through.  cosf/sinf are the accurate library functions.
+// The input is either qkv in the model dtype, or (parts != null) S float32 partial sums
+// of a split-K product, added here in the order s = 0, 1, ...
 template <typename T>
 __global__ void qk_norm_rope_kvwrite_kernel(
-    const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool,
+    const T* __restrict__ qkv, const float* __restrict__ parts, int S, size_t part_stride,
+    T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool,
     const float* __restrict__ q_gain, const float* __restrict__ k_gain,
     const float* __restrict__ inv_freq, int R, const int* __restrict__ positions,
     const int* __restrict__ token_rows, const int* __restrict__ block_table, int table_width,
@@ -116,11 +207,17 @@ __global__ void qk_norm_rope_kvwrite_kernel(
     const bool is_v = !is_q && !is_k;
     if (!is_q && !write_kv) return;
 
-    const T* src = qkv + ((size_t)n * n_heads + head) * D;
+    const size_t base = ((size_t)n * n_heads + head) * D;
     float* y = buf[warp];
     float ss = 0.f;
     for (int i = lane; i < D; i += 32) {
-        const float v = to_float(src[i]);
+        float v;
+        if (parts != nullptr) {
+            v = 0.f;
+            for (int s = 0; s < S; ++s) v += parts[s * part_stride + base + i];
+        } else {
+            v = to_float(qkv[base + i]);
+        }
         y[i] = v;
         ss += v * v;
     }
@@ -156,7 +253,104 @@ __global__ void qk_norm_rope_kvwrite_kernel(
     }
 }
 
-extern "C" int sb_qk_norm_rope_kvwrite(const void* qkv, void* q_out, void* k_pool, void* v_pool,
+// VPL consecutive elements of T as one aligned vector.
+template <typename T, int VPL> struct alignas(sizeof(T) * VPL) Pack { T v[VPL]; };
+
+// The same for head_dim = 32 * VPL with all dims rotating (R == D) or none (R == 0):
+// lane l owns elements l*VPL .. l*VPL+VPL-1, loads and stores them as one vector, and
+// finds its rotation partner (dim +- D/2) in lane l ^ 16.
+template <typename T, int VPL>
+__global__ void qk_norm_rope_kvwrite_fast_kernel(
+    const T* __restrict__ qkv, const float* __restrict__ parts, int S, size_t part_stride,
+    T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool,
+    const float* __restrict__ q_gain, const float* __restrict__ k_gain,
+    const float* __restrict__ inv_freq, int R, const int* __restrict__ positions,
+    const int* __restrict__ token_rows, const int* __restrict__ block_table, int table_width,
+    int BS, float eps, int Hq, int Hkv, int write_kv) {
+    constexpr int D = 32 * VPL;
+    const int n = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * 4 + warp;
+    const int n_heads = Hq + 2 * Hkv;
+    if (head >= n_heads) return;
+    const bool is_q = head < Hq;
+    const bool is_k = !is_q && head < Hq + Hkv;
+    const bool is_v = !is_q && !is_k;
+    if (!is_q && !write_kv) return;
+
+    const size_t base = ((size_t)n * n_heads + head) * D + lane * VPL;
+    float y[VPL];
+    if (parts != nullptr) {
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) y[i] = 0.f;
+        for (int s = 0; s < S; ++s) {
+            const Pack<float, VPL> p = *reinterpret_cast<const Pack<float, VPL>*>(parts + s * part_stride + base);
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) y[i] += p.v[i];
+        }
+    } else {
+        const Pack<T, VPL> p = *reinterpret_cast<const Pack<T, VPL>*>(qkv + base);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) y[i] = to_float(p.v[i]);
+    }
+    const int pos = positions[n];
+    const float* gain = is_q ? q_gain : (is_k ? k_gain : nullptr);
+    if (gain != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) ss += y[i] * y[i];
+        ss = warp_sum(ss);
+        const float rinv = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) y[i] = y[i] * rinv * gain[lane * VPL + i];
+    }
+    Pack<T, VPL> o;
+    if (!is_v && R == D) {
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const float partner = __shfl_xor_sync(0xffffffffu, y[i], 16);
+            const float ang = (float)pos * inv_freq[(lane & 15) * VPL + i];
+            const float c = cosf(ang), s = sinf(ang);
+            o.v[i] = from_float<T>(lane < 16 ? y[i] * c - partner * s : y[i] * c + partner * s);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) o.v[i] = from_float<T>(y[i]);
+    }
+    T* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)n * Hq + head) * D;
+    } else {
+        const int kh = is_k ? head - Hq : head - Hq - Hkv;
+        const int row = token_rows[n];
+        const int page = block_table[(size_t)row * table_width + pos / BS];
+        T* pool = is_k ? k_pool : v_pool;
+        dst = pool + (((size_t)page * Hkv + kh) * BS + (pos % BS)) * D;
+    }
+    *reinterpret_cast<Pack<T, VPL>*>(dst + lane * VPL) = o;
+}
+
+template <typename T>
+static void qk_launch(const void* qkv, const float* parts, int S, size_t part_stride, void* q_out, void* k_pool,
+                      void* v_pool, const float* q_gain, const float* k_gain, const float* inv_freq,
+                      int rotary_dim, const int* positions, const int* token_rows, const int* block_table,
+                      int table_width, int page_size, float eps, int Hq, int Hkv, int D, int N, int write_kv,
+                      cudaStream_t stream) {
+    dim3 grid(N, (Hq + 2 * Hkv + 3) / 4);
+    const bool fast = (rotary_dim == D || rotary_dim == 0) && (D == 64 || D == 128 || D == 256);
+#define SB_QK_ARGS (const T*)qkv, parts, S, part_stride, (T*)q_out, (T*)k_pool, (T*)v_pool, q_gain, k_gain, \
+                   inv_freq, rotary_dim, positions, token_rows, block_table, table_width, page_size, eps, Hq, Hkv
+    if (fast && D == 64) qk_norm_rope_kvwrite_fast_kernel<T, 2><<<grid, 128, 0, stream>>>(SB_QK_ARGS, write_kv);
+    else if (fast && D == 128) qk_norm_rope_kvwrite_fast_kernel<T, 4><<<grid, 128, 0, stream>>>(SB_QK_ARGS, write_kv);
+    else if (fast) qk_norm_rope_kvwrite_fast_kernel<T, 8><<<grid, 128, 0, stream>>>(SB_QK_ARGS, write_kv);
+    else qk_norm_rope_kvwrite_kernel<T><<<grid, 128, 0, stream>>>(SB_QK_ARGS, D, write_kv);
+#undef SB_QK_ARGS
+}
+
+// qkv: [N, (Hq+2Hkv)*D] in the model dtype, or null when `parts` (float32
+// [S, N, (Hq+2Hkv)*D], `part_stride` floats apart) holds split-K partial sums instead.
+extern "C" int sb_qk_norm_rope_kvwrite(const void* qkv, const float* parts, int S, long long part_stride,
+                                       void* q_out, void* k_pool, void* v_pool,
                                        const float* q_gain, const float* k_gain,
                                        const float* inv_freq, int rotary_dim, const int* positions,
                                        const int* token_rows, const int* block_table, int table_width,
@@ -168,17 +362,17 @@ extern "C" int sb_qk_norm_rope_kvwrite(const void* qkv, void* q_out, void* k_poo
                "qk_norm_rope: rotary_dim %d must be even and at most head_dim %d", rotary_dim, D);
     SB_REQUIRE(page_size > 0 && table_width > 0, "qk_norm_rope: bad page_size %d or table width %d",
                page_size, table_width);
+    SB_REQUIRE((qkv != nullptr) != (parts != nullptr), "qk_norm_rope: give qkv or partial sums, not both");
+    SB_REQUIRE(parts == nullptr || S >= 1, "qk_norm_rope: %d partial sums", S);
     if (N == 0) return 0;
-    dim3 grid(N, (Hq + 2 * Hkv + 3) / 4);
     if (dtype == SB_F32)
-        qk_norm_rope_kvwrite_kernel<float><<<grid, 128, 0, stream>>>(
-            (const float*)qkv, (float*)q_out, (float*)k_pool, (float*)v_pool, q_gain, k_gain, inv_freq,
-            rotary_dim, positions, token_rows, block_table, table_width, page_size, eps, Hq, Hkv, D, write_kv);
+        qk_launch<float>(qkv, parts, S, (size_t)part_stride, q_out, k_pool, v_pool, q_gain, k_gain, inv_freq,
+                         rotary_dim, positions, token_rows, block_table, table_width, page_size, eps, Hq, Hkv, D, N,
+                         write_kv, stream);
     else if (dtype == SB_BF16)
-        qk_norm_rope_kvwrite_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
-            (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
-            (__nv_bfloat16*)v_pool, q_gain, k_gain, inv_freq, rotary_dim, positions, token_rows,
-            block_table, table_width, page_size, eps, Hq, Hkv, D, write_kv);
+        qk_launch<__nv_bfloat16>(qkv, parts, S, (size_t)part_stride, q_out, k_pool, v_pool, q_gain, k_gain,
+                                 inv_freq, rotary_dim, positions, token_rows, block_table, table_width, page_size,
+                                 eps, Hq, Hkv, D, N, write_kv, stream);
     else
         SB_REQUIRE(false, "qk_norm_rope: unknown dtype %d", dtype);
     SB_LAUNCH_CHECK();
@@ -198,10 +392,58 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ in, s
     }
 }
 
+// F a multiple of the 16-byte vector width: one vector of gate and one of up per thread.
+template <typename T>
+__global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ in, size_t total_vec, int F) {
+    constexpr int VEC = Vec16<T>::N;
+    const int fv = F / VEC;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vec;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = i / fv;
+        const int f = (int)(i - n * fv) * VEC;
+        Vec16<T> g, u;
+        g.load(in + n * 2 * F + f);
+        u.load(in + n * 2 * F + F + f);
+        float r[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            const float gv = g.get(e);
+            r[e] = u.get(e) * (gv / (1.0f + expf(-gv)));
+        }
+        T* o = out + n * F + f;
+        if constexpr (sizeof(T) == 2) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(r[2 * e], r[2 * e + 1]);
+                pk[e] = *reinterpret_cast<uint32_t*>(&v);
+            }
+            *reinterpret_cast<uint4*>(o) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        } else {
+            *reinterpret_cast<float4*>(o) = make_float4(r[0], r[1], r[2], r[3]);
+        }
+    }
+}
+
 extern "C" int sb_silu_mul(void* out, const void* gate_up, int N, int F, int dtype, cudaStream_t stream) {
     SB_REQUIRE(N >= 0 && F > 0, "silu_mul: bad sizes N=%d F=%d", N, F);
     if (N == 0) return 0;
     const size_t total = (size_t)N * F;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(gate_up)) & 15) == 0;
+    const int vec = dtype == SB_F32 ? 4 : 8;
+    if (aligned && F % vec == 0) {
+        const size_t total_vec = total / vec;
+        size_t blocks = (total_vec + 255) / 256;
+        if (blocks > 148 * 32) blocks = 148 * 32;
+        if (dtype == SB_F32)
+            silu_mul_vec_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)out, (const float*)gate_up, total_vec, F);
+        else if (dtype == SB_BF16)
+            silu_mul_vec_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(
+                (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, total_vec, F);
+        else
+            SB_REQUIRE(false, "silu_mul: unknown dtype %d", dtype);
+        SB_LAUNCH_CHECK();
+    }
     size_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == SB_F32)

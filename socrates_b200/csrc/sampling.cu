@@ -22,14 +22,25 @@ __device__ __forceinline__ float uniform_for(uint32_t key, uint32_t index) {
     return ((float)(x >> 9) + 0.5f) * (1.0f / 8388608.0f);
 }
 
+__device__ __forceinline__ bool better(float v, int i, float best, int best_i) {
+    return v > best || (v == best && i < best_i);
+}
+
 // temperature[m] == 0: argmax, ties to the lowest index.
 // temperature[m] > 0 : argmax_i (logit_i / T - log(-log u_i)).
+// grid (M, C): block c of row m scans one slice of the vocabulary and leaves its best
+// (score, index) in `scratch`; the block of a row that finishes last (a counter in
+// `scratch`) merges the C candidates and writes out[m].  The merge is an argmax over
+// exact values with the index as tie-break, so its order does not matter.
+//   scratch: int32 [M, 2*C + 1]; the counters (last entry of each row) are zero before
+//   the first call and are reset by the merging block.
 __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
                               const float* __restrict__ temperature, const uint32_t* __restrict__ seeds,
-                              const uint32_t* __restrict__ counters, int V) {
+                              const uint32_t* __restrict__ counters, int V, int* __restrict__ scratch) {
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
-    const int m = blockIdx.x;
+    __shared__ int s_last;
+    const int m = blockIdx.x, C = gridDim.y;
     const float* row = logits + (size_t)m * V;
     const float T = temperature ? temperature[m] : 0.f;
     uint32_t key = 0;
@@ -38,25 +49,28 @@ __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ l
         key = mix32(key ^ mix32(counters[m] + 0x85EBCA6Bu));
     }
     const float inv_t = T > 0.f ? 1.0f / T : 1.0f;
+    const int per = (V + C - 1) / C;
+    const int begin = blockIdx.y * per, end = min(V, begin + per);
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
         float v = row[i];
         if (T > 0.f) {
             const float u = uniform_for(key, (uint32_t)i);
             v = v * inv_t - logf(-logf(u));
         }
-        if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+        if (better(v, i, best, best_i)) { best = v; best_i = i; }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
         const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+        if (better(ov, oi, best, best_i)) { best = ov; best_i = oi; }
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) { s_val[warp] = best; s_idx[warp] = best_i; }
     __syncthreads();
+    int* mine = scratch + (size_t)m * (2 * C + 1);
     if (warp == 0) {
         const int nw = (blockDim.x + 31) >> 5;
         best = lane < nw ? s_val[lane] : -INFINITY;
@@ -65,21 +79,58 @@ __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ l
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best, o);
             const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-            if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+            if (better(ov, oi, best, best_i)) { best = ov; best_i = oi; }
         }
-        // A row of NaNs or -inf leaves best_i untouched; report index 0 rather than garbage.
-        if (lane == 0) out[m] = best_i == 0x7fffffff ? 0 : best_i;
+        if (lane == 0) {
+            mine[2 * blockIdx.y] = __float_as_int(best);
+            mine[2 * blockIdx.y + 1] = best_i;
+            __threadfence();
+            s_last = atomicAdd(&mine[2 * C], 1) == C - 1;
+        }
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (warp == 0) {
+        best = -INFINITY;
+        best_i = 0x7fffffff;
+        for (int c = lane; c < C; c += 32) {
+            const float v = __int_as_float(((volatile int*)mine)[2 * c]);
+            const int i = ((volatile int*)mine)[2 * c + 1];
+            if (better(v, i, best, best_i)) { best = v; best_i = i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (better(ov, oi, best, best_i)) { best = ov; best_i = oi; }
+        }
+        if (lane == 0) {
+            // A row of NaNs or -inf leaves best_i untouched; report index 0 rather than garbage.
+            out[m] = best_i == 0x7fffffff ? 0 : best_i;
+            mine[2 * C] = 0;
+        }
     }
 }
 
 }  // namespace
 
+// How many slices a row of V logits is cut into (so callers can size `scratch`).
+extern "C" int sb_sample_slices(int V) {
+    int c = (V + 8191) / 8192;
+    return c < 1 ? 1 : (c > 32 ? 32 : c);
+}
+
+// scratch: int32, at least M * (2 * sb_sample_slices(V) + 1) entries, zero before the first use.
 extern "C" int sb_sample(int* out, const float* logits, const float* temperature, const uint32_t* seeds,
-                         const uint32_t* counters, int M, int V, cudaStream_t stream) {
+                         const uint32_t* counters, int M, int V, int* scratch, cudaStream_t stream) {
     SB_REQUIRE(M >= 0 && V > 0, "sample: bad sizes M=%d V=%d", M, V);
     SB_REQUIRE(temperature == nullptr || (seeds != nullptr && counters != nullptr),
                "sample: temperature sampling needs seeds and counters");
+    SB_REQUIRE(scratch != nullptr, "sample: scratch is required");
+    SB_REQUIRE(M <= 65535 * 32, "sample: too many rows");
     if (M == 0) return 0;
-    sample_kernel<<<M, 1024, 0, stream>>>(out, logits, temperature, seeds, counters, V);
+    dim3 grid(M, sb_sample_slices(V));
+    sample_kernel<<<grid, 512, 0, stream>>>(out, logits, temperature, seeds, counters, V, scratch);
     SB_LAUNCH_CHECK();
 }

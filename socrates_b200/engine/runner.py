@@ -80,6 +80,8 @@ class ModelRunner:
         self._next = 0
         self.sampled = torch.zeros(max_tokens, dtype=torch.int32, device=self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.sample_scratch = torch.zeros(ops.sample_scratch_size(max_tokens, self.vocab), dtype=torch.int32,
+                                          device=self.device)
         self.use_graphs = use_graphs and model.supports_graph
         self._graphs: Dict[Tuple[int, int, bool], Tuple[torch.cuda.CUDAGraph, Optional[torch.Tensor]]] = {}
         self._eager_decode_done: set = set()
@@ -195,7 +197,7 @@ class ModelRunner:
             L, m = self.layout, self.dev_meta
             tokens = self.sampled[:M]
             ops.sample(tokens, logits, m[L.temp:L.temp + M].view(torch.float32),
-                       m[L.seed:L.seed + M], m[L.counter:L.counter + M])
+                       m[L.seed:L.seed + M], m[L.counter:L.counter + M], self.sample_scratch)
         return logits, tokens
 
     def prepare(self, entries: Sequence[StepEntry],

@@ -92,13 +92,19 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optiona
                          eps: float, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
     """Per-head norm, rotation and paged KV write for N tokens.
 
-    qkv [N, (Hq+2Hkv)*D]; q_out [N, Hq*D]; pools [pages, Hkv, BS, D] (None: the keys
-    and values of this step are not stored, the layer reads another layer's cache).
+    qkv [N, (Hq+2Hkv)*D] in the model dtype, or float32 [S, N, (Hq+2Hkv)*D] partial sums
+    of a split product (added here); q_out [N, Hq*D]; pools [pages, Hkv, BS, D] (None:
+    the keys and values of this step are not stored, the layer reads another layer's cache).
     """
-    N = qkv.shape[0]
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
-    _want(qkv, "qkv", None, (N, (Hq + 2 * Hkv) * D))
-    _want(q_out, "q_out", qkv.dtype, (N, Hq * D))
+    width = (Hq + 2 * Hkv) * D
+    parts = qkv.dim() == 3
+    N = qkv.shape[-2]
+    if parts:
+        _want(qkv, "qkv partial sums", torch.float32, (qkv.shape[0], N, width))
+    else:
+        _want(qkv, "qkv", q_out.dtype, (N, width))
+    _want(q_out, "q_out", None, (N, Hq * D))
     _want(positions, "positions", torch.int32, (N,))
     _want(token_rows, "token_rows", torch.int32, (N,))
     _want(block_table, "block_table", torch.int32)
@@ -108,8 +114,8 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optiona
     write_kv = k_pool is not None
     page_size = 1
     if write_kv:
-        _want(k_pool, "k_pool", qkv.dtype)
-        _want(v_pool, "v_pool", qkv.dtype, k_pool.shape)
+        _want(k_pool, "k_pool", q_out.dtype)
+        _want(v_pool, "v_pool", q_out.dtype, k_pool.shape)
         if k_pool.dim() != 4 or k_pool.shape[1] != Hkv or k_pool.shape[3] != D:
             raise KernelError(f"pools must be [pages, {Hkv}, page_size, {D}], got {tuple(k_pool.shape)}")
         page_size = k_pool.shape[2]
@@ -118,9 +124,10 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optiona
             _want(g, nm, torch.float32, (D,))
     lib = library()
     check(lib, lib.sb_qk_norm_rope_kvwrite(
-        _ptr(qkv), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(q_gain), _ptr(k_gain), _ptr(inv_freq),
+        None if parts else _ptr(qkv), _ptr(qkv) if parts else None, qkv.shape[0] if parts else 0,
+        N * width, _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(q_gain), _ptr(k_gain), _ptr(inv_freq),
         rotary_dim, _ptr(positions), _ptr(token_rows), _ptr(block_table), block_table.shape[1],
-        page_size, float(eps), Hq, Hkv, D, N, int(write_kv), _code(qkv.dtype), _stream()),
+        page_size, float(eps), Hq, Hkv, D, N, int(write_kv), _code(q_out.dtype), _stream()),
         "qk_norm_rope_kvwrite")
 
 
@@ -134,10 +141,20 @@ def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
           "silu_mul")
 
 
+def sample_scratch_size(M: int, V: int) -> int:
+    """int32 entries of scratch that `sample` needs for M rows of V logits."""
+    return M * (2 * library().sb_sample_slices(int(V)) + 1)
+
+
 def sample(out: torch.Tensor, logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
-           seeds: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None) -> None:
+           seeds: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None,
+           scratch: Optional[torch.Tensor] = None) -> None:
     """out[m] = argmax(logits[m]) where temperature[m] == 0 (or temperature is None),
-    else a draw from softmax(logits[m] / temperature[m]) fixed by (seeds[m], counters[m])."""
+    else a draw from softmax(logits[m] / temperature[m]) fixed by (seeds[m], counters[m]).
+
+    `scratch`: int32 with at least sample_scratch_size(M, V) entries that were zero before
+    its first use (the kernel leaves it ready for the next call); allocated here if None.
+    """
     M, V = logits.shape
     _want(logits, "logits", torch.float32)
     _want(out, "out", torch.int32, (M,))
@@ -145,9 +162,15 @@ def sample(out: torch.Tensor, logits: torch.Tensor, temperature: Optional[torch.
         _want(temperature, "temperature", torch.float32, (M,))
         _want(seeds, "seeds", torch.int32, (M,))
         _want(counters, "counters", torch.int32, (M,))
+    need = sample_scratch_size(M, V)
+    if scratch is None:
+        scratch = torch.zeros(need, dtype=torch.int32, device=logits.device)
+    _want(scratch, "scratch", torch.int32)
+    if scratch.numel() < need:
+        raise KernelError(f"sample scratch has {scratch.numel()} entries, {need} are needed")
     lib = library()
     check(lib, lib.sb_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(seeds), _ptr(counters),
-                             M, V, _stream()), "sample")
+                             M, V, _ptr(scratch), _stream()), "sample")
 
 
 def gemm_simt(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, splits: int = 1) -> None:

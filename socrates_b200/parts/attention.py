@@ -72,7 +72,7 @@ class GQAAttention(Part):
 
     def forward(self, ctx, x: torch.Tensor, cache) -> Branch:
         N = x.shape[0]
-        qkv = self.qkv(ctx, x, "qkv")
+        qkv = self.qkv(ctx, x, "qkv", out="model_or_partial")
         q = ctx.buffers.take("q", N, (self.Hq * self.D,), ctx.dtype)
         k_pool, v_pool = cache.pools()
         table = cache.block_table()

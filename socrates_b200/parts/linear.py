@@ -22,9 +22,13 @@ class Linear:
 
     def __call__(self, ctx, x: torch.Tensor, buffer: str, out: str = "model") -> torch.Tensor:
         """`out`: "model" -> [M, N] in the model dtype; "float32" -> [M, N] float32;
-        "partial" -> float32 [S, M, N]."""
+        "partial" -> float32 [S, M, N]; "model_or_partial" -> partial sums when the
+        product is cut along K (the weight-streaming regime), else the model dtype: for
+        consumers that can add the parts themselves."""
         M = x.shape[0]
         N = self.out_features
+        if out == "model_or_partial":
+            out = "partial" if ctx.gemm_splits(M, self.weight, x.dtype) > 1 else "model"
         if out == "model":
             y = ctx.buffers.take(buffer, M, (N,), ctx.dtype)
         elif out == "float32":

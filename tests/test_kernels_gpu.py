@@ -133,7 +133,8 @@ def paged_case(rows_len, BS, Hkv, D, dtype, spare=5, seed=0):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("Hq,Hkv,D,R", [(6, 3, 48, 48), (5, 5, 16, 16), (8, 1, 128, 64), (4, 2, 80, 0)])
+@pytest.mark.parametrize("Hq,Hkv,D,R", [(6, 3, 48, 48), (5, 5, 16, 16), (8, 1, 128, 64), (4, 2, 80, 0),
+                                        (4, 2, 128, 128), (6, 2, 64, 64), (2, 1, 256, 256), (4, 4, 128, 0)])
 def test_qk_norm_rope_kvwrite(ops, ref, dtype, Hq, Hkv, D, R):
     BS, eps = 16, 1e-5
     lens = [33, 16, 5]
@@ -166,6 +167,31 @@ def test_qk_norm_rope_kvwrite(ops, ref, dtype, Hq, Hkv, D, R):
     ops.qk_norm_rope_kvwrite(qkv, q2, None, None, qg, kg, inv_freq, R, positions, token_rows, table,
                              eps, Hq, Hkv, D)
     assert torch.equal(q2, q_out)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("D", [32, 128])
+def test_qk_norm_rope_from_partial_sums(ops, ref, dtype, D):
+    """The split-K partial sums of the QKV product are added inside the kernel."""
+    Hq, Hkv, BS, S = 4, 2, 16, 5
+    k_pool, v_pool, table = paged_case([20], BS, Hkv, D, dtype)
+    N = 6
+    token_rows = torch.zeros(N, dtype=torch.int32, device=DEV)
+    positions = torch.arange(14, 20, dtype=torch.int32, device=DEV)
+    parts = rand(S, N, (Hq + 2 * Hkv) * D, seed=8)
+    qg, kg = 1 + 0.1 * rand(D, seed=6), 1 + 0.1 * rand(D, seed=7)
+    inv_freq = (1.0 / (1e4 ** (torch.arange(0, D, 2).float() / D))).to(DEV)
+    q_out = torch.empty(N, Hq * D, dtype=dtype, device=DEV)
+    ops.qk_norm_rope_kvwrite(parts, q_out, k_pool, v_pool, qg, kg, inv_freq, D, positions, token_rows, table,
+                             1e-6, Hq, Hkv, D)
+    total = parts[0]
+    for s in range(1, S):
+        total = total + parts[s]
+    q, k, v = ref.qk_norm_rope_ref(total, qg, kg, inv_freq, D, positions, 1e-6, Hq, Hkv, D)
+    page, off = ref.kv_slots(table, token_rows, positions, BS)
+    assert torch.allclose(q_out.float().view(N, Hq, D), q, **tol(dtype))
+    assert torch.allclose(k_pool[page, :, off].float(), k, **tol(dtype))
+    assert torch.allclose(v_pool[page, :, off].float(), v, **tol(dtype))
 
 
 def test_rotation_far_positions_float32(ops, ref):
@@ -320,6 +346,34 @@ def test_attention_refuses_bad_sizes(ops):
 
 
 # ---------------------------------------------------------------------------- sampling
+SCRATCH = None
+
+
+@pytest.fixture(autouse=True)
+def _scratch():
+    global SCRATCH
+    if SCRATCH is None and torch.cuda.is_available():
+        SCRATCH = torch.zeros(64 * 1024, dtype=torch.int32, device=DEV)
+    yield
+
+
+def test_sample_large_vocabulary_many_slices(ops):
+    """A vocabulary that is cut into several slices per row; the winner sits in each slice in turn."""
+    M, V = 7, 151936
+    logits = rand(M, V)
+    want = []
+    for m in range(M):
+        i = (m * 25013 + 7) % V
+        logits[m, i] = 30.0
+        want.append(i)
+    logits[3, 5] = 30.0                              # an earlier slice holds an equal value: lowest index wins
+    want[3] = min(want[3], 5)
+    out = torch.empty(M, dtype=torch.int32, device=DEV)
+    for _ in range(3):                               # the scratch counters must be left ready for the next call
+        ops.sample(out, logits, scratch=SCRATCH)
+        assert out.tolist() == want
+
+
 def test_sample_greedy_ties_and_sizes(ops):
     M, V = 5, 1337
     logits = rand(M, V)
