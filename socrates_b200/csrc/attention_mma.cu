@@ -76,21 +76,30 @@ template <int D> __device__ __forceinline__ int tile_off(int row, int chunk) {
     return row * D + ((chunk ^ x) << 3);
 }
 
-// Bring keys [tile_start, tile_start + 64) of one KV head into shared memory.  Rows of
-// keys outside [lo, hi) are zero-filled and never read from the pool.
-template <int D>
+// Bring keys [tile_start, tile_start + KTILE) of one KV head into shared memory.  Rows of
+// keys outside [lo, hi) are zero-filled and never read from the pool.  `table` maps the
+// logical page (pos >> bs_log2) - table_base to the physical page; it is a shared-memory
+// copy of the block-table segment the block needs, so that no copy waits on a global
+// table read.  A thread always copies the same 16-byte column of the rows it serves, so
+// its address arithmetic per row is a shift, a mask and a table read.
+template <int D, int KTILE = KT, int NTHR = THREADS>
 __device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const bf16* __restrict__ k_pool,
-                                             const bf16* __restrict__ v_pool, const int* __restrict__ table,
-                                             int BS, int Hkv, int kh, int tile_start, int lo, int hi) {
-    constexpr int CH = D / 8;
-    for (int idx = threadIdx.x; idx < KT * CH; idx += THREADS) {
-        const int key = idx / CH, c = idx - key * CH;
+                                             const bf16* __restrict__ v_pool, const int* table, int table_base,
+                                             int bs_log2, int Hkv, int kh, int tile_start, int lo, int hi) {
+    constexpr int CH = D / 8;                       // 16-byte columns of a row
+    constexpr int ROWS = NTHR / CH;                 // rows served per pass
+    static_assert(NTHR % CH == 0, "threads must tile the columns");
+    const int c = threadIdx.x % CH;
+    const int r0 = threadIdx.x / CH;
+    const int bs_mask = (1 << bs_log2) - 1;
+#pragma unroll
+    for (int key = r0; key < KTILE; key += ROWS) {
         const int pos = tile_start + key;
         const bool valid = pos >= lo && pos < hi;
         size_t src = 0;
         if (valid) {
-            const int page = table[pos / BS];
-            src = (((size_t)page * Hkv + kh) * BS + (pos % BS)) * D + c * 8;
+            const int page = table[(pos >> bs_log2) - table_base];
+            src = ((((size_t)page * Hkv + kh) << bs_log2) + (pos & bs_mask)) * D + c * 8;
         }
         const int off = tile_off<D>(key, c);
         cp_async16(smem_u32(ks + off), k_pool + src, valid ? 16 : 0);
@@ -216,8 +225,10 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf
     bf16* qs = reinterpret_cast<bf16*>(smem);               // [64][D]
     bf16* kbuf = qs + 64 * D;                               // 2 x [64][D]
     bf16* vbuf = kbuf + 2 * KT * D;                         // 2 x [64][D]
+    int* stab = reinterpret_cast<int*>(vbuf + 2 * KT * D);  // the pages of keys [lo, hi): up to table_width
 
     const int G = Hq / Hkv;
+    const int bs_log2 = 31 - __clz(BS);                     // the page size is a power of two
     const int TQ = 64 / G;                                  // tokens per tile
     const int kh = blockIdx.y;
     // ---- which request, which tile
@@ -238,6 +249,9 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf
     const int hi = first_pos + n_tok;                       // keys [lo, hi) are needed by this tile
     const int lo = (window > 0 && first_pos + 1 > window) ? first_pos + 1 - window : 0;
     const int tile_begin = lo / KT, tile_end = (hi + KT - 1) / KT;
+    const int table_base = lo / BS;
+    for (int i = threadIdx.x; i <= (hi - 1) / BS - table_base; i += THREADS) stab[i] = table[table_base + i];
+    __syncthreads();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // ---- Q tile: row = token * G + head
@@ -249,7 +263,7 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf
         const bf16* src = q + ((size_t)(t0 + (valid ? tok : 0)) * Hq + kh * G + g) * D + c * 8;
         cp_async16(smem_u32(qs + tile_off<D>(row, c)), src, valid ? 16 : 0);
     }
-    load_kv_tile<D>(kbuf, vbuf, k_pool, v_pool, table, BS, Hkv, kh, tile_begin * KT, lo, hi);
+    load_kv_tile<D>(kbuf, vbuf, k_pool, v_pool, stab, table_base, bs_log2, Hkv, kh, tile_begin * KT, lo, hi);
     cp_async_commit();
 
     int qpos[2], qlo[2];
@@ -268,8 +282,8 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf
     for (int i = 0; i < n_tiles; ++i) {
         const int buf = i & 1;
         if (i + 1 < n_tiles) {
-            load_kv_tile<D>(kbuf + (buf ^ 1) * KT * D, vbuf + (buf ^ 1) * KT * D, k_pool, v_pool, table, BS, Hkv,
-                            kh, (tile_begin + i + 1) * KT, lo, hi);
+            load_kv_tile<D>(kbuf + (buf ^ 1) * KT * D, vbuf + (buf ^ 1) * KT * D, k_pool, v_pool, stab, table_base,
+                            bs_log2, Hkv, kh, (tile_begin + i + 1) * KT, lo, hi);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -304,20 +318,25 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf
 
 // ----------------------------------------------------------------------------- decode
 // grid (Hkv, N, NP); every token is one query at position positions[n] of row token_rows[n].
-template <int D>
-__global__ void __launch_bounds__(THREADS)
+// NW warps; a key tile holds 16 keys per warp; S stages of tiles are kept in flight.
+template <int D, int NW, int S>
+__global__ void __launch_bounds__(32 * NW)
 attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                    const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                    const int* __restrict__ block_table, int table_width, const int* __restrict__ token_rows,
                    const int* __restrict__ positions, int Hq, int Hkv, int BS, int window, float scale_log2,
                    int NP) {
+    constexpr int KTD = 16 * NW;                            // keys per tile
+    constexpr int NTHR = 32 * NW;
     extern __shared__ __align__(128) uint8_t smem[];
     bf16* qs = reinterpret_cast<bf16*>(smem);               // [16][D]
-    bf16* kbuf = qs + 16 * D;                               // 2 x [64][D]
-    bf16* vbuf = kbuf + 2 * KT * D;
-    __shared__ float w_m[4][16], w_l[4][16];
+    bf16* kbuf = qs + 16 * D;                               // S x [KTD][D]
+    bf16* vbuf = kbuf + S * KTD * D;                        // S x [KTD][D]
+    int* stab = reinterpret_cast<int*>(vbuf + S * KTD * D); // the pages of this partition: up to table_width
+    __shared__ float w_m[NW][16], w_l[NW][16];
 
     const int G = Hq / Hkv;
+    const int bs_log2 = 31 - __clz(BS);                     // the page size is a power of two
     const int kh = blockIdx.x, n = blockIdx.y, part = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pos = positions[n];
@@ -340,46 +359,52 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         }
         return;
     }
-    const int tile_begin = k_begin / KT, tile_end = (k_end + KT - 1) / KT;
+    const int tile_begin = k_begin / KTD, tile_end = (k_end + KTD - 1) / KTD;
+    const int n_tiles = tile_end - tile_begin;
+    for (int i = threadIdx.x; i < pg_end - pg_begin; i += NTHR) stab[i] = table[pg_begin + i];
+    __syncthreads();
     constexpr int CH = D / 8;
-    for (int idx = threadIdx.x; idx < 16 * CH; idx += THREADS) {
+    for (int idx = threadIdx.x; idx < 16 * CH; idx += NTHR) {
         const int row = idx / CH, c = idx - row * CH;
         const bool valid = row < G;
         const bf16* src = q + ((size_t)n * Hq + h0 + (valid ? row : 0)) * D + c * 8;
         cp_async16(smem_u32(qs + tile_off<D>(row, c)), src, valid ? 16 : 0);
     }
-    load_kv_tile<D>(kbuf, vbuf, k_pool, v_pool, table, BS, Hkv, kh, tile_begin * KT, k_begin, k_end);
-    cp_async_commit();
+#pragma unroll
+    for (int s = 0; s < S - 1; ++s) {
+        if (s < n_tiles)
+            load_kv_tile<D, KTD, NTHR>(kbuf + s * KTD * D, vbuf + s * KTD * D, k_pool, v_pool, stab, pg_begin,
+                                       bs_log2, Hkv, kh, (tile_begin + s) * KTD, k_begin, k_end);
+        cp_async_commit();
+    }
 
     const int qpos[2] = {pos, pos};
     const int qlo[2] = {lo, lo};
     RowState<D> st;
     st.init();
     uint32_t qf[D / 16][4];
-    const int n_tiles = tile_end - tile_begin;
     for (int i = 0; i < n_tiles; ++i) {
-        const int buf = i & 1;
-        if (i + 1 < n_tiles) {
-            load_kv_tile<D>(kbuf + (buf ^ 1) * KT * D, vbuf + (buf ^ 1) * KT * D, k_pool, v_pool, table, BS, Hkv,
-                            kh, (tile_begin + i + 1) * KT, k_begin, k_end);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
+        cp_async_wait<S - 2>();                             // tile i has landed (this thread's share)
+        __syncthreads();                                    // ... and everybody's; slot (i-1)%S is free
+        const int nxt = i + S - 1;
+        if (nxt < n_tiles)
+            load_kv_tile<D, KTD, NTHR>(kbuf + (nxt % S) * KTD * D, vbuf + (nxt % S) * KTD * D, k_pool, v_pool,
+                                       stab, pg_begin, bs_log2, Hkv, kh, (tile_begin + nxt) * KTD, k_begin, k_end);
+        cp_async_commit();
         if (i == 0) {
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk)
                 ldmatrix_x4(qf[kk], smem_u32(qs + tile_off<D>(lane & 15, kk * 2 + (lane >> 4))));
         }
         // warp w takes keys 16w .. 16w+15 of the tile
-        warp_tile<D, 16>(st, qf, kbuf + buf * KT * D, vbuf + buf * KT * D, warp * 16, (tile_begin + i) * KT, qpos,
-                         qlo, k_begin, k_end, scale_log2);
-        __syncthreads();
+        const int buf = i % S;
+        warp_tile<D, 16>(st, qf, kbuf + buf * KTD * D, vbuf + buf * KTD * D, warp * 16, (tile_begin + i) * KTD,
+                         qpos, qlo, k_begin, k_end, scale_log2);
     }
-    // ---- merge the four warps: each writes its rows' (m, l, O) to shared memory
-    float* wo = reinterpret_cast<float*>(kbuf);             // [4][16][D] floats: fits in the K and V buffers
+    cp_async_wait<0>();
+    __syncthreads();
+    // ---- merge the warps: each writes its rows' (m, l, O) to shared memory
+    float* wo = reinterpret_cast<float*>(kbuf);             // [NW][16][D] floats: fits in the K and V buffers
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         float l = st.l[i];
@@ -395,15 +420,15 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < G * D; idx += THREADS) {
+    for (int idx = threadIdx.x; idx < G * D; idx += NTHR) {
         const int row = idx / D, d = idx - row * D;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w)
+        for (int w = 0; w < NW; ++w)
             if (w_l[w][row] > 0.f) M = fmaxf(M, w_m[w][row]);
         float L = 0.f, o = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < NW; ++w) {
             if (w_l[w][row] > 0.f) {
                 const float f = exp2f((w_m[w][row] - M) * scale_log2);
                 L += f * w_l[w][row];
@@ -425,7 +450,8 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
 }
 
 template <int D> constexpr int prefill_smem() { return (64 * D + 4 * KT * D) * 2; }
-template <int D> constexpr int decode_smem() { return (16 * D + 4 * KT * D) * 2; }
+template <int D, int NW, int S> constexpr int decode_smem() { return (16 * D + 2 * S * 16 * NW * D) * 2; }
+constexpr int kMaxTableWidth = 4096;                         // entries of the staged block-table segment
 
 template <int D>
 int launch_prefill(void* out, const void* q, const void* k_pool, const void* v_pool, const int* block_table,
@@ -434,31 +460,34 @@ int launch_prefill(void* out, const void* q, const void* k_pool, const void* v_p
     auto kernel = attn_prefill_kernel<D>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, prefill_smem<D>());
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             prefill_smem<D>() + kMaxTableWidth * 4);
         if (e != cudaSuccess) { sb_set_error("attention_mma: %s", cudaGetErrorString(e)); return (int)e; }
         configured = true;
     }
     const int TQ = 64 / (Hq / Hkv);
     dim3 grid(N / TQ + R, Hkv);                              // an upper bound of the number of tiles
-    kernel<<<grid, THREADS, prefill_smem<D>(), stream>>>(
+    kernel<<<grid, THREADS, prefill_smem<D>() + table_width * 4, stream>>>(
         (bf16*)out, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, table_width, seq_starts,
         seq_rows, seq_first_pos, R, Hq, Hkv, BS, window, scale * LOG2E);
     return 0;
 }
 
-template <int D>
-int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool, const void* v_pool,
-                  const int* block_table, int table_width, const int* token_rows, const int* positions, int N,
-                  int Hq, int Hkv, int BS, int window, float scale, int NP, cudaStream_t stream) {
-    auto kernel = attn_decode_kernel<D>;
+template <int D, int NW, int S>
+int launch_decode_v(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool, const void* v_pool,
+                    const int* block_table, int table_width, const int* token_rows, const int* positions, int N,
+                    int Hq, int Hkv, int BS, int window, float scale, int NP, cudaStream_t stream) {
+    auto kernel = attn_decode_kernel<D, NW, S>;
+    constexpr int smem = decode_smem<D, NW, S>();
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, decode_smem<D>());
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             smem + kMaxTableWidth * 4);
         if (e != cudaSuccess) { sb_set_error("attention_mma: %s", cudaGetErrorString(e)); return (int)e; }
         configured = true;
     }
     dim3 grid(Hkv, N, NP);
-    kernel<<<grid, THREADS, decode_smem<D>(), stream>>>(
+    kernel<<<grid, 32 * NW, smem + table_width * 4, stream>>>(
         (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
         table_width, token_rows, positions, Hq, Hkv, BS, window, scale * LOG2E, NP);
     if (NP > 1) {
@@ -468,13 +497,34 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
     return 0;
 }
 
+// Shapes of the decode kernel: (warps, stages).  Variant 0 is the default.
+constexpr int kDecodeVariants = 5;
+constexpr int kVariantWarps[kDecodeVariants] = {4, 4, 2, 2, 4};
+constexpr int kVariantStages[kDecodeVariants] = {3, 2, 4, 6, 4};
+
+template <int D>
+int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool, const void* v_pool,
+                  const int* block_table, int table_width, const int* token_rows, const int* positions, int N,
+                  int Hq, int Hkv, int BS, int window, float scale, int NP, cudaStream_t stream, int variant = 0) {
+#define SB_DEC(NW, S) launch_decode_v<D, NW, S>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, \
+                                                token_rows, positions, N, Hq, Hkv, BS, window, scale, NP, stream)
+    switch (variant) {
+        case 1: return SB_DEC(4, 2);
+        case 2: return SB_DEC(2, 4);
+        case 3: return SB_DEC(2, 6);
+        case 4: return SB_DEC(4, 4);
+        default: return SB_DEC(4, 3);
+    }
+#undef SB_DEC
+}
+
 }  // namespace
 
 // 1 if the tensor-core kernels take this shape (bfloat16 only), else 0.
 extern "C" int sb_attention_mma_supports(int Hq, int Hkv, int D, int page_size, int decode) {
     if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return 0;
     if (!(D == 16 || D == 32 || D == 64 || D == 128)) return 0;
-    if (page_size <= 0) return 0;
+    if (page_size <= 0 || (page_size & (page_size - 1))) return 0;     // a power of two
     const int G = Hq / Hkv;
     return decode ? (G <= 16) : (64 % G == 0);
 }
@@ -489,6 +539,8 @@ extern "C" int sb_attention_prefill_mma(void* out, const void* q, const void* k_
     SB_REQUIRE(sb_attention_mma_supports(Hq, Hkv, D, page_size, 0),
                "attention_mma (prefill): Hq=%d Hkv=%d head_dim=%d is not supported", Hq, Hkv, D);
     SB_REQUIRE(R > 0 && N > 0 && window >= 0 && table_width > 0, "attention_mma: bad sizes R=%d N=%d", R, N);
+    SB_REQUIRE(table_width <= kMaxTableWidth, "attention_mma: block table of %d pages per row exceeds %d",
+               table_width, kMaxTableWidth);
     int rc;
     switch (D) {
         case 16: rc = launch_prefill<16>(out, q, k_pool, v_pool, block_table, table_width, seq_starts, seq_rows, seq_first_pos, R, N, Hq, Hkv, page_size, window, scale, stream); break;
@@ -500,24 +552,36 @@ extern "C" int sb_attention_prefill_mma(void* out, const void* q, const void* k_
     SB_LAUNCH_CHECK();
 }
 
+// Blocks of the decode kernel that fit one SM at a time (shared memory is the limit):
+// what the caller sizes the number of key partitions with.
+extern "C" int sb_attention_decode_mma_blocks_per_sm(int D, int variant) {
+    if (variant < 0 || variant >= kDecodeVariants) variant = 0;
+    const int smem = (16 * D + 2 * kVariantStages[variant] * 16 * kVariantWarps[variant] * D) * 2 + 1024 + 2048;
+    int b = (227 * 1024) / smem;
+    return b < 1 ? 1 : (b > 16 ? 16 : b);
+}
+
 // Steps in which every request brings one token.  Scratch as for sb_attention_simt.
+// `variant` selects (warps, stages) of the kernel; 0 is the default.
 extern "C" int sb_attention_decode_mma(void* out, float* part_o, float* part_ml, const void* q,
                                        const void* k_pool, const void* v_pool, const int* block_table,
                                        int table_width, const int* token_rows, const int* positions, int N,
                                        int Hq, int Hkv, int D, int page_size, int window, float scale,
-                                       int num_partitions, cudaStream_t stream) {
+                                       int num_partitions, int variant, cudaStream_t stream) {
     SB_REQUIRE(sb_attention_mma_supports(Hq, Hkv, D, page_size, 1),
                "attention_mma (decode): Hq=%d Hkv=%d head_dim=%d is not supported", Hq, Hkv, D);
     SB_REQUIRE(N > 0 && N <= 65535 && window >= 0 && table_width > 0, "attention_mma: bad sizes N=%d", N);
+    SB_REQUIRE(table_width <= kMaxTableWidth, "attention_mma: block table of %d pages per row exceeds %d",
+               table_width, kMaxTableWidth);
     SB_REQUIRE(num_partitions >= 1 && num_partitions <= 65535, "attention_mma: %d partitions", num_partitions);
     SB_REQUIRE(num_partitions == 1 || (part_o != nullptr && part_ml != nullptr),
                "attention_mma: split over %d partitions needs scratch buffers", num_partitions);
     int rc;
     switch (D) {
-        case 16: rc = launch_decode<16>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream); break;
-        case 32: rc = launch_decode<32>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream); break;
-        case 64: rc = launch_decode<64>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream); break;
-        default: rc = launch_decode<128>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream); break;
+        case 16: rc = launch_decode<16>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant); break;
+        case 32: rc = launch_decode<32>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant); break;
+        case 64: rc = launch_decode<64>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant); break;
+        default: rc = launch_decode<128>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant); break;
     }
     if (rc != 0) return rc;
     SB_LAUNCH_CHECK();
@@ -543,8 +607,8 @@ extern "C" int sb_attention_decode_mma_noalloc(void* out, const void* q, const v
                                                int num_partitions, cudaStream_t stream) {
     SB_REQUIRE(sb_attention_mma_supports(query_heads, kv_heads, head_dim, page_size, 1),
                "attention (no-alloc): Hq=%d Hkv=%d head_dim=%d is not supported", query_heads, kv_heads, head_dim);
-    SB_REQUIRE(tokens > 0 && tokens <= 65535 && window >= 0 && table_width > 0,
-               "attention (no-alloc): bad sizes tokens=%d", tokens);
+    SB_REQUIRE(tokens > 0 && tokens <= 65535 && window >= 0 && table_width > 0 && table_width <= kMaxTableWidth,
+               "attention (no-alloc): bad sizes tokens=%d table_width=%d", tokens, table_width);
     SB_REQUIRE(num_partitions >= 1 && num_partitions <= 65535, "attention (no-alloc): %d partitions",
                num_partitions);
     const long long slots = (long long)tokens * query_heads * num_partitions;

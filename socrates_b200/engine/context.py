@@ -123,17 +123,18 @@ class StepContext:
         else:
             ops.gemm_simt(out, x, w, splits=S)
 
-    def attention_partitions(self, num_kv_heads: int, page_size: int, keys_per_part: int) -> int:
+    def attention_partitions(self, num_kv_heads: int, blocks_per_sm: int, keys_per_part: int) -> int:
         """Into how many key partitions each query's keys are cut.
 
         A function of static quantities only (batch width, limits), so that a recorded
-        graph stays valid: enough blocks to fill the SMs twice, never less than
-        `keys_per_part` keys of the longest possible row in a partition.
+        graph stays valid: as many partitions as keep every block resident at once (one
+        wave, no tail), at most 16, never less than `keys_per_part` keys of the longest
+        possible row in a partition.
         """
         blocks = max(1, num_kv_heads * self.num_tokens)
-        want = -(-2 * self.num_sms // blocks)
+        want = (self.num_sms * blocks_per_sm) // blocks
         most = max(1, -(-self.max_context // keys_per_part))
-        return max(1, min(want, most, 64))
+        return max(1, min(want, most, 16))
 
     def attention(self, out, q, k_pool, v_pool, table, num_heads: int, scale: float, window: int) -> None:
         """Causal attention of every token of the step over its row's pages.
@@ -150,7 +151,10 @@ class StepContext:
                                       self.seq_first_pos, num_heads, scale, window)
             return
         use_mma = tensor_cores and self.all_decode and ops.attention_mma_supports(num_heads, Hkv, D, page_size, True)
-        NP = self.attention_partitions(Hkv, page_size, 256 if use_mma else 4 * page_size)
+        if use_mma:
+            NP = self.attention_partitions(Hkv, ops.attention_decode_mma_blocks_per_sm(D), 128)
+        else:
+            NP = self.attention_partitions(Hkv, 4, 4 * page_size)
         part_o = part_ml = None
         if NP > 1:
             part_o = self.buffers.take_flat("attn_part_o", N * num_heads * NP * D, torch.float32)

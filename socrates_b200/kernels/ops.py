@@ -296,9 +296,10 @@ def attention_decode_mma(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
                          block_table: torch.Tensor, token_rows: torch.Tensor, positions: torch.Tensor,
                          num_heads: int, scale: float, window: int = 0, num_partitions: int = 1,
                          part_o: Optional[torch.Tensor] = None,
-                         part_ml: Optional[torch.Tensor] = None) -> None:
+                         part_ml: Optional[torch.Tensor] = None, variant: int = 0) -> None:
     """Paged attention of single decode tokens on the tensor cores (bfloat16), the keys
-    of each token cut into `num_partitions` parts; arguments as `attention_simt`."""
+    of each token cut into `num_partitions` parts; arguments as `attention_simt`.
+    `variant` picks the kernel's (warps, stages); 0 is the default."""
     N = q.shape[0]
     _, Hkv, BS, D = k_pool.shape
     Hq = num_heads
@@ -318,5 +319,10 @@ def attention_decode_mma(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
     check(lib, lib.sb_attention_decode_mma(
         _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
         block_table.shape[1], _ptr(token_rows), _ptr(positions), N, Hq, Hkv, D, BS, int(window),
-        float(scale), num_partitions, _stream()), "attention_decode_mma",
+        float(scale), num_partitions, int(variant), _stream()), "attention_decode_mma",
         kernels=2 if num_partitions > 1 else 1)
+
+
+def attention_decode_mma_blocks_per_sm(head_dim: int, variant: int = 0) -> int:
+    """Blocks of the decode attention kernel that are resident on one SM at a time."""
+    return library().sb_attention_decode_mma_blocks_per_sm(int(head_dim), int(variant))
