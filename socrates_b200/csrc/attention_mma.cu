@@ -221,6 +221,8 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf
                     const int* __restrict__ seq_starts, const int* __restrict__ seq_rows,
                     const int* __restrict__ seq_first_pos, int R, int Hq, int Hkv, int BS, int window,
                     float scale_log2) {
+    sb::pdl_launch_dependents();     // the next kernel may begin its prologue
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     extern __shared__ __align__(128) uint8_t smem[];
     bf16* qs = reinterpret_cast<bf16*>(smem);               // [64][D]
     bf16* kbuf = qs + 64 * D;                               // 2 x [64][D]
@@ -326,6 +328,8 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
                    const int* __restrict__ block_table, int table_width, const int* __restrict__ token_rows,
                    const int* __restrict__ positions, int Hq, int Hkv, int BS, int window, float scale_log2,
                    int NP) {
+    sb::pdl_launch_dependents();     // the next kernel may begin its prologue
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     constexpr int KTD = 16 * NW;                            // keys per tile
     constexpr int NTHR = 32 * NW;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -467,7 +471,7 @@ int launch_prefill(void* out, const void* q, const void* k_pool, const void* v_p
     }
     const int TQ = 64 / (Hq / Hkv);
     dim3 grid(N / TQ + R, Hkv);                              // an upper bound of the number of tiles
-    kernel<<<grid, THREADS, prefill_smem<D>() + table_width * 4, stream>>>(
+    sb::launch(kernel, grid, dim3(THREADS), prefill_smem<D>() + table_width * 4, stream,
         (bf16*)out, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, table_width, seq_starts,
         seq_rows, seq_first_pos, R, Hq, Hkv, BS, window, scale * LOG2E);
     return 0;
@@ -487,12 +491,12 @@ int launch_decode_v(void* out, float* part_o, float* part_ml, const void* q, con
         configured = true;
     }
     dim3 grid(Hkv, N, NP);
-    kernel<<<grid, 32 * NW, smem + table_width * 4, stream>>>(
+    sb::launch(kernel, dim3(grid), dim3(32 * NW), smem + table_width * 4, stream, 
         (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
         table_width, token_rows, positions, Hq, Hkv, BS, window, scale * LOG2E, NP);
     if (NP > 1) {
         dim3 rgrid(Hq, N);
-        attn_reduce_kernel<bf16><<<rgrid, 128, 0, stream>>>((bf16*)out, part_o, part_ml, Hq, D, NP);
+        sb::launch(attn_reduce_kernel<bf16>, dim3(rgrid), dim3(128), 0, stream, (bf16*)out, part_o, part_ml, Hq, D, NP);
     }
     return 0;
 }

@@ -13,6 +13,8 @@ namespace sb {
 template <typename T>
 __global__ void attn_reduce_kernel(T* __restrict__ out, const float* __restrict__ part_o,
                                    const float* __restrict__ part_ml, int Hq, int D, int NP) {
+    sb::pdl_launch_dependents();     // the next kernel may begin its prologue
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     const int h = blockIdx.x, n = blockIdx.y;
     const size_t base = ((size_t)n * Hq + h) * NP;
     float M = -INFINITY;

@@ -31,6 +31,8 @@ attn_tokens_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __res
                    const int* __restrict__ block_table, int table_width,
                    const int* __restrict__ token_rows, const int* __restrict__ positions, int Hq,
                    int Hkv, int D, int BS, int window, float scale, int NP) {
+    sb::pdl_launch_dependents();     // the next kernel may begin its prologue
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     __shared__ float qs[GMAX][256];
     __shared__ float sc[GMAX][CHUNK];
     __shared__ float s_m[GMAX], s_l[GMAX], s_alpha[GMAX];
@@ -176,12 +178,12 @@ void launch(void* out, float* part_o, float* part_ml, const void* q, const void*
             const int* positions, int N, int Hq, int Hkv, int D, int BS, int window, float scale, int NP,
             cudaStream_t stream) {
     dim3 grid(Hkv, N, NP);
-    attn_tokens_kernel<T><<<grid, THREADS, 0, stream>>>(
+    sb::launch(attn_tokens_kernel<T>, dim3(grid), dim3(THREADS), 0, stream, 
         (T*)out, part_o, part_ml, (const T*)q, (const T*)k_pool, (const T*)v_pool, block_table,
         table_width, token_rows, positions, Hq, Hkv, D, BS, window, scale, NP);
     if (NP > 1) {
         dim3 rgrid(Hq, N);
-        attn_reduce_kernel<T><<<rgrid, 128, 0, stream>>>((T*)out, part_o, part_ml, Hq, D, NP);
+        sb::launch(attn_reduce_kernel<T>, dim3(rgrid), dim3(128), 0, stream, (T*)out, part_o, part_ml, Hq, D, NP);
     }
 }
 

@@ -39,6 +39,36 @@ void sb_set_error(const char* fmt, ...);
 
 namespace sb {
 
+// Programmatic dependent launch.  Every kernel of the library is launched with the
+// "programmatic stream serialization" attribute: it may start while the kernel before it
+// in the stream is still running.  `pdl_launch_dependents()` lets the NEXT kernel start
+// its own prologue; `pdl_wait()` returns once every earlier kernel has completed and its
+// writes are visible.  Before pdl_wait() a kernel touches only memory no kernel of the
+// step writes (weights, gains, tables of constants) and its own shared/tensor memory;
+// it reads activations and writes anything global only after it.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+bool pdl_enabled();    // host: false when SOCRATES_PDL=0
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float to_float(float x) { return x; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
 

@@ -11,6 +11,8 @@ using namespace sb;
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table,
                              const int* __restrict__ ids, int d, int V) {
+    sb::pdl_launch_dependents();     // the next kernel may begin its prologue
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     const int n = blockIdx.x;
     int id = ids[n];
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);   // ids are validated on the host; stay in bounds regardless
@@ -23,6 +25,8 @@ __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ tabl
 template <typename T>
 __global__ void embed_vec_kernel(float* __restrict__ out, const T* __restrict__ table,
                                  const int* __restrict__ ids, int d, int V) {
+    sb::pdl_launch_dependents();     // the next kernel may begin its prologue
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     constexpr int VEC = Vec16<T>::N;
     const int n = blockIdx.x;
     int id = ids[n];
@@ -44,13 +48,13 @@ extern "C" int sb_embed(float* out, const void* table, const int* ids, int N, in
     if (N == 0) return 0;
     const bool aligned = (reinterpret_cast<uintptr_t>(table) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     if (dtype == SB_F32) {
-        if (aligned && d % 4 == 0) embed_vec_kernel<float><<<N, 256, 0, stream>>>(out, (const float*)table, ids, d, V);
-        else embed_kernel<float><<<N, 256, 0, stream>>>(out, (const float*)table, ids, d, V);
+        if (aligned && d % 4 == 0) sb::launch(embed_vec_kernel<float>, dim3(N), dim3(256), 0, stream, out, (const float*)table, ids, d, V);
+        else sb::launch(embed_kernel<float>, dim3(N), dim3(256), 0, stream, out, (const float*)table, ids, d, V);
     } else if (dtype == SB_BF16) {
         if (aligned && d % 8 == 0)
-            embed_vec_kernel<__nv_bfloat16><<<N, 256, 0, stream>>>(out, (const __nv_bfloat16*)table, ids, d, V);
+            sb::launch(embed_vec_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, out, (const __nv_bfloat16*)table, ids, d, V);
         else
-            embed_kernel<__nv_bfloat16><<<N, 256, 0, stream>>>(out, (const __nv_bfloat16*)table, ids, d, V);
+            sb::launch(embed_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, out, (const __nv_bfloat16*)table, ids, d, V);
     } else {
         SB_REQUIRE(false, "embed: unknown dtype %d", dtype);
     }
@@ -70,6 +74,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
                                    int S, size_t delta_stride, const float* __restrict__ gain,
                                    T* __restrict__ out, const int* __restrict__ row_index, int d,
                                    float eps, int write_residual) {
+    sb::pdl_launch_dependents();     // the next kernel may begin its prologue
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     extern __shared__ float row[];          // d floats
     __shared__ float scratch[33];
     const int m = blockIdx.x;
@@ -97,6 +103,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const float
                                        int S, size_t delta_stride, const float* __restrict__ gain,
                                        T* __restrict__ out, const int* __restrict__ row_index, int d,
                                        float eps, int write_residual) {
+    sb::pdl_launch_dependents();     // the next kernel may begin its prologue
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     extern __shared__ float row[];          // d floats
     __shared__ float scratch[33];
     const int m = blockIdx.x;
@@ -110,6 +118,13 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const float
     for (int i = threadIdx.x; i < d4; i += blockDim.x) {
         float4 v = res4[i];
         int s = 0;
+        for (; s + 8 <= S; s += 8) {                 // eight independent loads in flight, added in order
+            float4 p[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) p[j] = __ldg(del4 + (s + j) * stride4 + i);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { v.x += p[j].x; v.y += p[j].y; v.z += p[j].z; v.w += p[j].w; }
+        }
         for (; s + 4 <= S; s += 4) {
             const float4 a = __ldg(del4 + (s + 0) * stride4 + i), b = __ldg(del4 + (s + 1) * stride4 + i);
             const float4 c = __ldg(del4 + (s + 2) * stride4 + i), e = __ldg(del4 + (s + 3) * stride4 + i);
@@ -157,12 +172,19 @@ extern "C" int sb_add_rmsnorm(float* residual, const float* delta, int S, long l
     const bool vec = d % 4 == 0 && delta_stride % 4 == 0 &&
                      ((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(delta) |
                        reinterpret_cast<uintptr_t>(gain) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
-    const int threads = vec ? (d >= 4096 ? 512 : 256) : (d >= 2048 ? 512 : 256);
+    // vector kernel: one float4 column per thread where the row allows it (few rows are the
+    // decode regime, where the S partial sums of a column should all be in flight at once)
+    int threads = d >= 2048 ? 512 : 256;
+    if (vec) {
+        threads = ((d / 4 + 31) / 32) * 32;
+        if (threads > 1024) threads = 1024;
+        if (M > 512 && threads > 256) threads = 256;
+    }
 #define SB_NORM_LAUNCH(KERNEL, T)                                                                        \
     do {                                                                                                  \
         if (smem > 48 * 1024)                                                                             \
             cudaFuncSetAttribute(KERNEL<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-        KERNEL<T><<<M, threads, smem, stream>>>(residual, delta, S, (size_t)delta_stride, gain, (T*)out,  \
+        sb::launch(KERNEL<T>, dim3(M), dim3(threads), smem, stream, residual, delta, S, (size_t)delta_stride, gain, (T*)out,  \
                                                 row_index, d, eps, write_residual);                      \
     } while (0)
     if (dtype == SB_F32) {
@@ -196,6 +218,8 @@ __global__ void qk_norm_rope_kvwrite_kernel(
     const float* __restrict__ inv_freq, int R, const int* __restrict__ positions,
     const int* __restrict__ token_rows, const int* __restrict__ block_table, int table_width,
     int BS, float eps, int Hq, int Hkv, int D, int write_kv) {
+    sb::pdl_launch_dependents();     // the next kernel may begin its prologue
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     __shared__ float buf[4][256];
     const int n = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -267,6 +291,8 @@ __global__ void qk_norm_rope_kvwrite_fast_kernel(
     const float* __restrict__ inv_freq, int R, const int* __restrict__ positions,
     const int* __restrict__ token_rows, const int* __restrict__ block_table, int table_width,
     int BS, float eps, int Hq, int Hkv, int write_kv) {
+    sb::pdl_launch_dependents();     // the next kernel may begin its prologue
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     constexpr int D = 32 * VPL;
     const int n = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -340,10 +366,10 @@ static void qk_launch(const void* qkv, const float* parts, int S, size_t part_st
     const bool fast = (rotary_dim == D || rotary_dim == 0) && (D == 64 || D == 128 || D == 256);
 #define SB_QK_ARGS (const T*)qkv, parts, S, part_stride, (T*)q_out, (T*)k_pool, (T*)v_pool, q_gain, k_gain, \
                    inv_freq, rotary_dim, positions, token_rows, block_table, table_width, page_size, eps, Hq, Hkv
-    if (fast && D == 64) qk_norm_rope_kvwrite_fast_kernel<T, 2><<<grid, 128, 0, stream>>>(SB_QK_ARGS, write_kv);
-    else if (fast && D == 128) qk_norm_rope_kvwrite_fast_kernel<T, 4><<<grid, 128, 0, stream>>>(SB_QK_ARGS, write_kv);
-    else if (fast) qk_norm_rope_kvwrite_fast_kernel<T, 8><<<grid, 128, 0, stream>>>(SB_QK_ARGS, write_kv);
-    else qk_norm_rope_kvwrite_kernel<T><<<grid, 128, 0, stream>>>(SB_QK_ARGS, D, write_kv);
+    if (fast && D == 64) sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, 2>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv);
+    else if (fast && D == 128) sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, 4>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv);
+    else if (fast) sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, 8>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv);
+    else sb::launch(qk_norm_rope_kvwrite_kernel<T>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, D, write_kv);
 #undef SB_QK_ARGS
 }
 
@@ -382,6 +408,8 @@ extern "C" int sb_qk_norm_rope_kvwrite(const void* qkv, const float* parts, int 
 // SiLU*mul: out[n, f] = up * gate * sigmoid(gate), gate = in[n, f], up = in[n, F + f].
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ in, size_t total, int F) {
+    sb::pdl_launch_dependents();     // the next kernel may begin its prologue
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
         const size_t n = i / F;
@@ -395,6 +423,8 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ in, s
 // F a multiple of the 16-byte vector width: one vector of gate and one of up per thread.
 template <typename T>
 __global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ in, size_t total_vec, int F) {
+    sb::pdl_launch_dependents();     // the next kernel may begin its prologue
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     constexpr int VEC = Vec16<T>::N;
     const int fv = F / VEC;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vec;
@@ -436,9 +466,9 @@ extern "C" int sb_silu_mul(void* out, const void* gate_up, int N, int F, int dty
         size_t blocks = (total_vec + 255) / 256;
         if (blocks > 148 * 32) blocks = 148 * 32;
         if (dtype == SB_F32)
-            silu_mul_vec_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)out, (const float*)gate_up, total_vec, F);
+            sb::launch(silu_mul_vec_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (float*)out, (const float*)gate_up, total_vec, F);
         else if (dtype == SB_BF16)
-            silu_mul_vec_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(
+            sb::launch(silu_mul_vec_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, 
                 (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, total_vec, F);
         else
             SB_REQUIRE(false, "silu_mul: unknown dtype %d", dtype);
@@ -447,9 +477,9 @@ extern "C" int sb_silu_mul(void* out, const void* gate_up, int N, int F, int dty
     size_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == SB_F32)
-        silu_mul_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)out, (const float*)gate_up, total, F);
+        sb::launch(silu_mul_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (float*)out, (const float*)gate_up, total, F);
     else if (dtype == SB_BF16)
-        silu_mul_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(
+        sb::launch(silu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, 
             (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, total, F);
     else
         SB_REQUIRE(false, "silu_mul: unknown dtype %d", dtype);

@@ -16,6 +16,8 @@ template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(TC* __restrict__ C, const TA* __restrict__ A, const TW* __restrict__ W, int M, int N,
                  int K, int k_per_split) {
+    sb::pdl_launch_dependents();     // the next kernel may begin its prologue
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -71,7 +73,7 @@ template <typename TA, typename TW, typename TC>
 void launch(void* C, const void* A, const void* W, int M, int N, int K, int splits, cudaStream_t stream) {
     const int k_per_split = ((K + splits - 1) / splits + BK - 1) / BK * BK;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, splits);
-    gemm_simt_kernel<TA, TW, TC><<<grid, 256, 0, stream>>>((TC*)C, (const TA*)A, (const TW*)W, M, N, K,
+    sb::launch(gemm_simt_kernel<TA, TW, TC>, dim3(grid), dim3(256), 0, stream, (TC*)C, (const TA*)A, (const TW*)W, M, N, K,
                                                            k_per_split);
 }
 

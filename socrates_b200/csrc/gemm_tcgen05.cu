@@ -165,12 +165,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     tcgen05_fence_after();
     const uint32_t tmem_d = tmem_base_slot;
 
+    sb::pdl_launch_dependents();          // the next kernel may begin its prologue
     if (warp == 0 && lane == 0) {
-        // ---------------- producer: TMA loads into the ring
-        int issued = 0;
-        for (int i = 0; i < kb_count; ++i) {
+        // ---------------- producer: TMA loads into the ring.
+        // The weight operand (tma_a when SWAP, else tma_b) is written by no kernel, so its
+        // tiles of the first ring-full of stages are fetched BEFORE the wait on the previous
+        // kernel; the activation tiles of those stages follow after it.
+        const int ahead = min(kb_count, STAGES);
+        for (int i = 0; i < ahead; ++i) {
+            const uint32_t bar = smem_u32(&full_bar[i]);
+            const uint32_t sa = tiles + i * stage_bytes<BN>();
+            const uint32_t sb_ = sa + BM * BK * 2;
+            mbar_arrive_expect_tx(bar, stage_bytes<BN>());
+            if (SWAP) tma_load_2d(sa, &tma_a, bar, (kb_begin + i) * BK, a0);
+            else tma_load_2d(sb_, &tma_b, bar, (kb_begin + i) * BK, b0);
+        }
+        sb::pdl_wait();
+        for (int i = 0; i < ahead; ++i) {
+            const uint32_t bar = smem_u32(&full_bar[i]);
+            const uint32_t sa = tiles + i * stage_bytes<BN>();
+            const uint32_t sb_ = sa + BM * BK * 2;
+            if (SWAP) tma_load_2d(sb_, &tma_b, bar, (kb_begin + i) * BK, b0);
+            else tma_load_2d(sa, &tma_a, bar, (kb_begin + i) * BK, a0);
+        }
+        int issued = ahead;
+        for (int i = ahead; i < kb_count; ++i) {
             const int s = i % STAGES;
-            if (i >= STAGES && !mbar_wait(smem_u32(&empty_bar[s]), ((i / STAGES) - 1) & 1)) {
+            if (!mbar_wait(smem_u32(&empty_bar[s]), ((i / STAGES) - 1) & 1)) {
                 atomicExch(status, 1);
                 atomicExch(&abort_flag, 1);
                 break;
@@ -178,10 +199,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             if (*((volatile int*)&abort_flag)) break;
             const uint32_t bar = smem_u32(&full_bar[s]);
             const uint32_t sa = tiles + s * stage_bytes<BN>();
-            const uint32_t sb = sa + BM * BK * 2;
+            const uint32_t sb_ = sa + BM * BK * 2;
             mbar_arrive_expect_tx(bar, stage_bytes<BN>());
             tma_load_2d(sa, &tma_a, bar, (kb_begin + i) * BK, a0);
-            tma_load_2d(sb, &tma_b, bar, (kb_begin + i) * BK, b0);
+            tma_load_2d(sb_, &tma_b, bar, (kb_begin + i) * BK, b0);
             issued = i + 1;
         }
         if (*((volatile int*)&abort_flag)) {
@@ -217,6 +238,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     __syncwarp();
 
     // ---------------- epilogue: all four warps, warp w owns lanes 32w .. 32w+31
+    sb::pdl_wait();                       // C may still be read by an earlier kernel until now
     bool good = mbar_wait(smem_u32(&accum_bar), 0);
     if (!good) atomicExch(status, 3);
     if (*((volatile int*)&abort_flag)) good = false;
@@ -349,7 +371,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, 
         if (e != cudaSuccess) { sb_set_error("gemm_tcgen05: %s", cudaGetErrorString(e)); return (int)e; }
         configured = true;
     }
-    kernel<<<grid, 128, smem, stream>>>(ma, mb, (TC*)C, M, N, K, kb_per_split, status);
+    sb::launch(kernel, dim3(grid), dim3(128), smem, stream, ma, mb, (TC*)C, M, N, K, kb_per_split, status);
     return 0;
 }
 

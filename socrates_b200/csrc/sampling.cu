@@ -37,6 +37,8 @@ __device__ __forceinline__ bool better(float v, int i, float best, int best_i) {
 __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
                               const float* __restrict__ temperature, const uint32_t* __restrict__ seeds,
                               const uint32_t* __restrict__ counters, int V, int* __restrict__ scratch) {
+    sb::pdl_launch_dependents();     // the next kernel may begin its prologue
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     __shared__ int s_last;
@@ -131,6 +133,6 @@ extern "C" int sb_sample(int* out, const float* logits, const float* temperature
     SB_REQUIRE(M <= 65535 * 32, "sample: too many rows");
     if (M == 0) return 0;
     dim3 grid(M, sb_sample_slices(V));
-    sample_kernel<<<grid, 512, 0, stream>>>(out, logits, temperature, seeds, counters, V, scratch);
+    sb::launch(sample_kernel, dim3(grid), dim3(512), 0, stream, out, logits, temperature, seeds, counters, V, scratch);
     SB_LAUNCH_CHECK();
 }
