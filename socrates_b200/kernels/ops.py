@@ -230,7 +230,7 @@ def gemm_tcgen05_splits(K: int, splits: int) -> int:
 
 
 def gemm_tcgen05(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, status: torch.Tensor,
-                 splits: int = 1) -> int:
+                 splits: int = 1, variant: int = 0) -> int:
     """out = a @ w.T on the tcgen05 tensor cores; a [M, K] and w [N, K] bfloat16, K % 8 == 0.
 
     out is bfloat16 or float32 [M, N], or float32 [S, M, N] partial sums where S =
@@ -252,7 +252,7 @@ def gemm_tcgen05(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, status: to
     lib = library()
     s_io = ctypes.c_int(S)
     check(lib, lib.sb_gemm_tcgen05(_ptr(out), _ptr(a), _ptr(w), M, N, K, _code(out.dtype),
-                                   ctypes.byref(s_io), _ptr(status), _stream()), "gemm_tcgen05")
+                                   ctypes.byref(s_io), _ptr(status), int(variant), _stream()), "gemm_tcgen05")
     if s_io.value != S:
         raise KernelError(f"gemm_tcgen05 wrote {s_io.value} parts where {S} were expected")
     return S
