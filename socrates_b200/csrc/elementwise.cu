@@ -405,24 +405,28 @@ extern "C" int sb_qk_norm_rope_kvwrite(const void* qkv, const float* parts, int 
 }
 
 // ----------------------------------------------------------------------------------------
-// SiLU*mul: out[n, f] = up * gate * sigmoid(gate), gate = in[n, f], up = in[n, F + f].
+// SiLU*mul: out[n, f] = up * gate * sigmoid(gate).  Two layouts of the input row of 2F:
+// concatenated (gate = in[n, f], up = in[n, F + f]) or interleaved (gate = in[n, 2f],
+// up = in[n, 2f + 1]; the layout of a product with interleaved gate/up weight rows).
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ in, size_t total, int F) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ in, size_t total, int F,
+                                int interleaved) {
     sb::pdl_launch_dependents();     // the next kernel may begin its prologue
     sb::pdl_wait();                  // everything before this kernel is complete and visible
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
         const size_t n = i / F;
         const int f = (int)(i - n * F);
-        const float g = to_float(in[n * 2 * F + f]);
-        const float u = to_float(in[n * 2 * F + F + f]);
+        const float g = to_float(in[n * 2 * F + (interleaved ? 2 * f : f)]);
+        const float u = to_float(in[n * 2 * F + (interleaved ? 2 * f + 1 : F + f)]);
         out[i] = from_float<T>(u * (g / (1.0f + expf(-g))));
     }
 }
 
 // F a multiple of the 16-byte vector width: one vector of gate and one of up per thread.
 template <typename T>
-__global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ in, size_t total_vec, int F) {
+__global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ in, size_t total_vec, int F,
+                                    int interleaved) {
     sb::pdl_launch_dependents();     // the next kernel may begin its prologue
     sb::pdl_wait();                  // everything before this kernel is complete and visible
     constexpr int VEC = Vec16<T>::N;
@@ -432,13 +436,24 @@ __global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ i
         const size_t n = i / fv;
         const int f = (int)(i - n * fv) * VEC;
         Vec16<T> g, u;
-        g.load(in + n * 2 * F + f);
-        u.load(in + n * 2 * F + F + f);
         float r[VEC];
+        if (interleaved) {          // two consecutive vectors hold VEC (gate, up) pairs
+            g.load(in + n * 2 * F + 2 * f);
+            u.load(in + n * 2 * F + 2 * f + VEC);
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-            const float gv = g.get(e);
-            r[e] = u.get(e) * (gv / (1.0f + expf(-gv)));
+            for (int e = 0; e < VEC; ++e) {
+                const float gv = e < VEC / 2 ? g.get(2 * e) : u.get(2 * e - VEC);
+                const float uv = e < VEC / 2 ? g.get(2 * e + 1) : u.get(2 * e + 1 - VEC);
+                r[e] = uv * (gv / (1.0f + expf(-gv)));
+            }
+        } else {
+            g.load(in + n * 2 * F + f);
+            u.load(in + n * 2 * F + F + f);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                const float gv = g.get(e);
+                r[e] = u.get(e) * (gv / (1.0f + expf(-gv)));
+            }
         }
         T* o = out + n * F + f;
         if constexpr (sizeof(T) == 2) {
@@ -455,7 +470,8 @@ __global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ i
     }
 }
 
-extern "C" int sb_silu_mul(void* out, const void* gate_up, int N, int F, int dtype, cudaStream_t stream) {
+extern "C" int sb_silu_mul(void* out, const void* gate_up, int N, int F, int interleaved, int dtype,
+                           cudaStream_t stream) {
     SB_REQUIRE(N >= 0 && F > 0, "silu_mul: bad sizes N=%d F=%d", N, F);
     if (N == 0) return 0;
     const size_t total = (size_t)N * F;
@@ -466,10 +482,10 @@ extern "C" int sb_silu_mul(void* out, const void* gate_up, int N, int F, int dty
         size_t blocks = (total_vec + 255) / 256;
         if (blocks > 148 * 32) blocks = 148 * 32;
         if (dtype == SB_F32)
-            sb::launch(silu_mul_vec_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (float*)out, (const float*)gate_up, total_vec, F);
+            sb::launch(silu_mul_vec_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (float*)out, (const float*)gate_up, total_vec, F, interleaved);
         else if (dtype == SB_BF16)
             sb::launch(silu_mul_vec_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, 
-                (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, total_vec, F);
+                (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, total_vec, F, interleaved);
         else
             SB_REQUIRE(false, "silu_mul: unknown dtype %d", dtype);
         SB_LAUNCH_CHECK();
@@ -477,10 +493,10 @@ extern "C" int sb_silu_mul(void* out, const void* gate_up, int N, int F, int dty
     size_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == SB_F32)
-        sb::launch(silu_mul_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (float*)out, (const float*)gate_up, total, F);
+        sb::launch(silu_mul_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (float*)out, (const float*)gate_up, total, F, interleaved);
     else if (dtype == SB_BF16)
         sb::launch(silu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, 
-            (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, total, F);
+            (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, total, F, interleaved);
     else
         SB_REQUIRE(false, "silu_mul: unknown dtype %d", dtype);
     SB_LAUNCH_CHECK();

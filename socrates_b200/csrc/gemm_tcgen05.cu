@@ -300,6 +300,226 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     }
 }
 
+// ----------------------------------------------------------------------------- persistent kernel
+// Many rows (prompt portions): one block per SM walks over output tiles of 128 x BN.
+// Six warps: warp 0 lane 0 feeds the shared-memory ring by TMA, warp 1 lane 0 issues the
+// MMAs, warps 2-5 read finished accumulators out of tensor memory and store C.  There are
+// two accumulators (TMEM columns 0.. and 256..), so the epilogue of tile i runs beside the
+// main loop of tile i+1.  Tiles are walked with the row index fastest: blocks running at
+// the same time share the weight panel, which stays in L2.
+//   EPI = 0: C[m, n] = acc
+//   EPI = 1: the weight rows interleave gate and up (row 2f = gate_f, row 2f+1 = up_f);
+//            C[m, f] = up * silu(gate), C has N/2 columns (SiLU*mul fused into the product).
+constexpr int ACC_STRIDE = 256;          // TMEM columns between the two accumulators
+
+template <int BN, int STAGES, typename TC, int EPI>
+__global__ void __launch_bounds__(192)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                               TC* __restrict__ C, int M, int N, int K, int tiles_m, int tiles_n,
+                               int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[STAGES];
+    __shared__ __align__(8) uint64_t acc_full[2];
+    __shared__ __align__(8) uint64_t acc_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int kb_total = (K + BK - 1) / BK;
+    const int n_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&acc_full[a]), 1);
+            mbar_init(smem_u32(&acc_empty[a]), 4);      // one arrival per epilogue warp
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_d = tmem_base_slot;
+    sb::pdl_launch_dependents();
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- producer
+        // The weight tiles (tma_b) of the first ring-full are fetched before the wait on the
+        // previous kernel, the activation tiles after it.
+        uint32_t it = 0;                                   // k-blocks issued so far, over all tiles
+        bool waited = false;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            const int a0 = (t % tiles_m) * BM, b0 = (t / tiles_m) * BN;
+            if (!waited) {
+                const int ahead = min(kb_total, STAGES);
+                for (int i = 0; i < ahead; ++i) {
+                    const uint32_t bar = smem_u32(&full_bar[i]);
+                    mbar_arrive_expect_tx(bar, stage_bytes<BN>());
+                    tma_load_2d(tiles + i * stage_bytes<BN>() + BM * BK * 2, &tma_b, bar, i * BK, b0);
+                }
+                sb::pdl_wait();
+                for (int i = 0; i < ahead; ++i)
+                    tma_load_2d(tiles + i * stage_bytes<BN>(), &tma_a, smem_u32(&full_bar[i]), i * BK, a0);
+                waited = true;
+                it = ahead;
+                for (int i = ahead; i < kb_total && ok; ++i, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / STAGES) - 1) & 1)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&full_bar[s]);
+                    mbar_arrive_expect_tx(bar, stage_bytes<BN>());
+                    tma_load_2d(tiles + s * stage_bytes<BN>(), &tma_a, bar, i * BK, a0);
+                    tma_load_2d(tiles + s * stage_bytes<BN>() + BM * BK * 2, &tma_b, bar, i * BK, b0);
+                }
+                continue;
+            }
+            for (int i = 0; i < kb_total && ok; ++i, ++it) {
+                const int s = it % STAGES;
+                if (it >= STAGES && !mbar_wait(smem_u32(&empty_bar[s]), ((it / STAGES) - 1) & 1)) { ok = false; break; }
+                if (*((volatile int*)&abort_flag)) { ok = false; break; }
+                const uint32_t bar = smem_u32(&full_bar[s]);
+                mbar_arrive_expect_tx(bar, stage_bytes<BN>());
+                tma_load_2d(tiles + s * stage_bytes<BN>(), &tma_a, bar, i * BK, a0);
+                tma_load_2d(tiles + s * stage_bytes<BN>() + BM * BK * 2, &tma_b, bar, i * BK, b0);
+            }
+        }
+        if (!ok) {
+            atomicExch(status, 1);
+            atomicExch(&abort_flag, 1);
+            // Wait (bounded) for the copies in flight, so that none lands after exit.
+            for (uint32_t i = it > STAGES ? it - STAGES : 0; i < it; ++i)
+                mbar_wait(smem_u32(&full_bar[i % STAGES]), (i / STAGES) & 1);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer
+        constexpr uint32_t idesc = make_idesc(BN);
+        uint32_t it = 0;
+        int j = 0;                                         // tiles done by this block
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++j) {
+            const int acc = j & 1;
+            // the epilogue must have drained this accumulator (first use of each passes at once)
+            if (j >= 2 && !mbar_wait(smem_u32(&acc_empty[acc]), ((j >> 1) - 1) & 1)) { ok = false; break; }
+            tcgen05_fence_after();
+            const uint32_t d = tmem_d + acc * ACC_STRIDE;
+            for (int i = 0; i < kb_total; ++i, ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(smem_u32(&full_bar[s]), (it / STAGES) & 1)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t sa = tiles + s * stage_bytes<BN>();
+                const uint32_t sb_ = sa + BM * BK * 2;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    tcgen05_mma_bf16(d, make_smem_desc(sa + k * UMMA_K * 2), make_smem_desc(sb_ + k * UMMA_K * 2),
+                                     idesc, (i > 0 || k > 0) ? 1u : 0u);
+                tcgen05_commit(smem_u32(&empty_bar[s]));
+            }
+            if (!ok) break;
+            tcgen05_commit(smem_u32(&acc_full[acc]));
+        }
+        if (!ok) {
+            atomicExch(status, 2);
+            atomicExch(&abort_flag, 1);
+        }
+    } else if (warp >= 2) {
+        // ---------------- epilogue: warp w owns TMEM lanes 32*(w%4) .. +31
+        sb::pdl_wait();                                    // C may still be read by an earlier kernel until now
+        const int quarter = warp & 3;
+        int j = 0;
+        for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++j) {
+            const int acc = j & 1;
+            bool good = mbar_wait(smem_u32(&acc_full[acc]), (j >> 1) & 1);
+            if (*((volatile int*)&abort_flag)) good = false;
+            good = __all_sync(0xffffffffu, good);
+            if (!good) {
+                if (lane == 0) { atomicExch(status, 3); atomicExch(&abort_flag, 1); }
+                break;
+            }
+            tcgen05_fence_after();
+            const int a0 = (t % tiles_m) * BM, b0 = (t / tiles_m) * BN;
+            const int m = a0 + quarter * 32 + lane;
+            const uint32_t taddr = tmem_d + acc * ACC_STRIDE + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 2
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(taddr + c0, r);
+                tmem_ld_wait();
+                if (m >= M) continue;
+                if (EPI == 1) {
+                    // columns come in (gate, up) pairs: 16 accumulator columns -> 8 outputs
+                    const int f0 = (b0 + c0) >> 1, F = N >> 1;
+                    TC* row = C + (size_t)m * F + f0;
+                    float o[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        const float g = __uint_as_float(r[2 * q]), u = __uint_as_float(r[2 * q + 1]);
+                        o[q] = u * (g / (1.0f + expf(-g)));
+                    }
+                    if (f0 + 8 <= F && ((reinterpret_cast<uintptr_t>(row) & 15) == 0) && sizeof(TC) == 2) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            __nv_bfloat162 v = __floats2bfloat162_rn(o[2 * q], o[2 * q + 1]);
+                            pk[q] = *reinterpret_cast<uint32_t*>(&v);
+                        }
+                        *reinterpret_cast<uint4*>(row) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            if (f0 + q < F) store_out<TC>(row + q, o[q]);
+                    }
+                } else {
+                    TC* row = C + (size_t)m * N + b0 + c0;
+                    if (b0 + c0 + 16 <= N && ((reinterpret_cast<uintptr_t>(row) & 15) == 0)) {
+                        if constexpr (sizeof(TC) == 2) {
+                            uint32_t packed[8];
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * q]),
+                                                                         __uint_as_float(r[2 * q + 1]));
+                                packed[q] = *reinterpret_cast<uint32_t*>(&v);
+                            }
+                            uint4* dst = reinterpret_cast<uint4*>(row);
+                            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        } else {
+                            uint4* dst = reinterpret_cast<uint4*>(row);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+                                dst[q] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 16; ++q)
+                            if (b0 + c0 + q < N) store_out<TC>(row + q, __uint_as_float(r[q]));
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[acc])) : "memory");
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(512) : "memory");
+    }
+}
+
 // ----------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -375,15 +595,56 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, 
     return 0;
 }
 
+template <int BN, int STAGES, typename TC, int EPI>
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, int K, int* status,
+                      cudaStream_t stream) {
+    auto kernel = gemm_tcgen05_persistent_kernel<BN, STAGES, TC, EPI>;
+    constexpr int smem = STAGES * stage_bytes<BN>() + 1024;
+    static bool configured = false;
+    static int num_sms = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) { sb_set_error("gemm_tcgen05: %s", cudaGetErrorString(e)); return (int)e; }
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+        configured = true;
+    }
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    const int blocks = min(tiles_m * tiles_n, num_sms);
+    sb::launch(kernel, dim3(blocks), dim3(192), smem, stream, ma, mb, (TC*)C, M, N, K, tiles_m, tiles_n, status);
+    return 0;
+}
+
+// Tile width for many rows: the one whose last wave wastes least on 148 SMs.
+static int pick_bn(int M, int N) {
+    const int tiles_m = (M + BM - 1) / BM;
+    const int cands[3] = {256, 160, 128};
+    int best = 256;
+    long best_cost = -1;
+    for (int bn : cands) {
+        const long tiles = (long)tiles_m * ((N + bn - 1) / bn);
+        // waves x time of one tile; narrower tiles re-read more of A per flop, so they must
+        // win by a margin (8 % for 160, 15 % for 128) to be chosen
+        const long cost = ((tiles + 147) / 148) * bn * (bn == 256 ? 100 : (bn == 160 ? 108 : 115));
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
 template <typename TC>
 int dispatch(const void* A, const void* W, void* C, int M, int N, int K, int splits, int* status,
-             cudaStream_t stream, int* splits_out, int variant) {
+             cudaStream_t stream, int* splits_out, int variant, int epi) {
     const int kb_total = (K + BK - 1) / BK;
     if (splits > kb_total) splits = kb_total;
     const int kb_per_split = (kb_total + splits - 1) / splits;
     splits = (kb_total + kb_per_split - 1) / kb_per_split;      // no empty part
     *splits_out = splits;
     CUtensorMap ma, mb;
+    if (M <= 64 && epi != 0) {
+        sb_set_error("gemm_tcgen05: the fused SiLU*mul epilogue is for M > 64");
+        return SB_ERR_ARG;
+    }
     if (M <= 64) {
         const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
         if (!get_map(&ma, W, N, K, BM) || !get_map(&mb, A, M, K, bn)) {
@@ -405,6 +666,27 @@ int dispatch(const void* A, const void* W, void* C, int M, int N, int K, int spl
         return deep ? launch<64, 8, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream)
                     : launch<64, 4, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
     }
+    if (splits == 1 && N >= 128 && variant != 4) {
+        // the persistent kernel: one block per SM, epilogue beside the next tile's main loop
+        const int bn = pick_bn(M, N);
+        if (!get_map(&ma, A, M, K, BM) || !get_map(&mb, W, N, K, bn)) {
+            sb_set_error("gemm_tcgen05: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d)", M, N, K);
+            return SB_ERR_ARG;
+        }
+        if (epi == 1) {
+            if (bn == 256) return launch_persistent<256, 4, TC, 1>(ma, mb, C, M, N, K, status, stream);
+            if (bn == 160) return launch_persistent<160, 5, TC, 1>(ma, mb, C, M, N, K, status, stream);
+            return launch_persistent<128, 6, TC, 1>(ma, mb, C, M, N, K, status, stream);
+        }
+        if (bn == 256) return launch_persistent<256, 4, TC, 0>(ma, mb, C, M, N, K, status, stream);
+        if (bn == 160) return launch_persistent<160, 5, TC, 0>(ma, mb, C, M, N, K, status, stream);
+        return launch_persistent<128, 6, TC, 0>(ma, mb, C, M, N, K, status, stream);
+    }
+    if (epi != 0) {
+        sb_set_error("gemm_tcgen05: the fused SiLU*mul epilogue needs M > 64, N >= 128 and no K split");
+        return SB_ERR_ARG;
+    }
+    // variant 4: the one-tile-per-block kernel also for many rows
     const int bn = N >= 256 ? 256 : (N > 64 ? 128 : 64);
     if (!get_map(&ma, A, M, K, BM) || !get_map(&mb, W, N, K, bn)) {
         sb_set_error("gemm_tcgen05: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d)", M, N, K);
@@ -423,9 +705,12 @@ int dispatch(const void* A, const void* W, void* C, int M, int N, int K, int spl
 // *splits_io: wanted number of K parts in, number actually written out (never more).
 // status: device int the kernel writes a non-zero code to if a bounded wait gave up.
 // variant: 0 or 1 = shallow ring of the weight-streaming kernel (two blocks per SM),
-//          2 = deep ring (one block per SM).
+//          2 = deep ring (one block per SM); 4 = one tile per block also for many rows
+//          (the default there is the persistent kernel).
+// epilogue: 0 = C[M,N]; 1 = W interleaves gate and up rows and C is [M, N/2] = up * silu(gate)
+//          (many rows, no K split).
 extern "C" int sb_gemm_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, int c_dtype,
-                               int* splits_io, int* status, int variant, cudaStream_t stream) {
+                               int* splits_io, int* status, int variant, int epilogue, cudaStream_t stream) {
     SB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
     SB_REQUIRE(K % 8 == 0, "gemm_tcgen05: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
     SB_REQUIRE((reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(W) & 15) == 0,
@@ -434,12 +719,13 @@ extern "C" int sb_gemm_tcgen05(void* C, const void* A, const void* W, int M, int
     int splits = *splits_io;
     SB_REQUIRE(splits >= 1 && splits <= 64, "gemm_tcgen05: splits=%d is outside 1..64", splits);
     SB_REQUIRE(splits == 1 || c_dtype == SB_F32, "gemm_tcgen05: partial sums of a split product are float32");
+    SB_REQUIRE(epilogue == 0 || (epilogue == 1 && N % 2 == 0), "gemm_tcgen05: bad epilogue %d for N=%d", epilogue, N);
     SB_REQUIRE((M + 127) / 128 <= 65535 && (N + 63) / 64 <= 65535, "gemm_tcgen05: matrix too large");
     int rc;
     if (c_dtype == SB_F32)
-        rc = dispatch<float>(A, W, C, M, N, K, splits, status, stream, splits_io, variant);
+        rc = dispatch<float>(A, W, C, M, N, K, splits, status, stream, splits_io, variant, epilogue);
     else if (c_dtype == SB_BF16)
-        rc = dispatch<__nv_bfloat16>(A, W, C, M, N, K, splits, status, stream, splits_io, variant);
+        rc = dispatch<__nv_bfloat16>(A, W, C, M, N, K, splits, status, stream, splits_io, variant, epilogue);
     else
         SB_REQUIRE(false, "gemm_tcgen05: unknown output dtype %d", c_dtype);
     if (rc != 0) return rc;

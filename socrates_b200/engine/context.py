@@ -114,13 +114,21 @@ class StepContext:
         most = max(1, (-(-K // 64)) // 2)
         return ops.gemm_tcgen05_splits(K, min(want, most, 16))
 
-    def gemm(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> None:
-        """out = x w^T; out is [M, N] or float32 partial sums [S, M, N]."""
+    def can_fuse_silu_mul(self, M: int, w: torch.Tensor, x_dtype: torch.dtype) -> bool:
+        """Whether the product with an interleaved gate/up matrix can apply SiLU*mul in its
+        epilogue (the tensor-core kernel for many rows does)."""
+        return self.uses_tensor_cores(x_dtype, w) and M > 64 and w.shape[0] >= 128 and w.shape[0] % 2 == 0
+
+    def gemm(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, epilogue: int = 0) -> None:
+        """out = x w^T; out is [M, N] or float32 partial sums [S, M, N]; with epilogue 1 (see
+        can_fuse_silu_mul) out is [M, N/2] = up * silu(gate) of interleaved columns."""
         S = out.shape[0] if out.dim() == 3 else 1
         if self.uses_tensor_cores(x.dtype, w):
             ops.gemm_tcgen05(out if out.dim() == 3 and S > 1 else out.view(out.shape[-2], out.shape[-1]),
-                             x, w, self.status, S)
+                             x, w, self.status, S, epilogue=epilogue)
         else:
+            if epilogue:
+                raise ValueError("the fused epilogue exists only in the tensor-core kernel")
             ops.gemm_simt(out, x, w, splits=S)
 
     def attention_partitions(self, num_kv_heads: int, blocks_per_sm: int, keys_per_part: int) -> int:

@@ -30,12 +30,12 @@ _SIGNATURES = {
     "sb_embed": [P, P, P, I, I, I, I, P],
     "sb_add_rmsnorm": [P, P, I, LL, P, P, P, I, I, F, I, P],
     "sb_qk_norm_rope_kvwrite": [P, P, I, LL, P, P, P, P, P, P, I, P, P, P, I, I, F, I, I, I, I, I, I, P],
-    "sb_silu_mul": [P, P, I, I, I, P],
+    "sb_silu_mul": [P, P, I, I, I, I, P],
     "sb_sample": [P, P, P, P, P, I, I, P, P],
     "sb_sample_slices": [I],
     "sb_gemm_simt": [P, P, P, I, I, I, I, I, I, I, P],
     "sb_attention_simt": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P],
-    "sb_gemm_tcgen05": [P, P, P, I, I, I, I, P, P, I, P],
+    "sb_gemm_tcgen05": [P, P, P, I, I, I, I, P, P, I, I, P],
     "sb_gemm_tcgen05_splits": [I, I],
     "sb_attention_mma_supports": [I, I, I, I, I],
     "sb_attention_prefill_mma": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],

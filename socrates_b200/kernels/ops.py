@@ -131,13 +131,14 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optiona
         "qk_norm_rope_kvwrite")
 
 
-def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
-    """out[n, f] = gate_up[n, F + f] * silu(gate_up[n, f])."""
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, interleaved: bool = False) -> None:
+    """out[n, f] = up * silu(gate) with gate = gate_up[n, f], up = gate_up[n, F + f], or, when
+    `interleaved`, gate = gate_up[n, 2f], up = gate_up[n, 2f + 1]."""
     N, F2 = gate_up.shape
     _want(gate_up, "gate_up")
     _want(out, "out", gate_up.dtype, (N, F2 // 2))
     lib = library()
-    check(lib, lib.sb_silu_mul(_ptr(out), _ptr(gate_up), N, F2 // 2, _code(out.dtype), _stream()),
+    check(lib, lib.sb_silu_mul(_ptr(out), _ptr(gate_up), N, F2 // 2, int(interleaved), _code(out.dtype), _stream()),
           "silu_mul")
 
 
@@ -230,7 +231,7 @@ def gemm_tcgen05_splits(K: int, splits: int) -> int:
 
 
 def gemm_tcgen05(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, status: torch.Tensor,
-                 splits: int = 1, variant: int = 0) -> int:
+                 splits: int = 1, variant: int = 0, epilogue: int = 0) -> int:
     """out = a @ w.T on the tcgen05 tensor cores; a [M, K] and w [N, K] bfloat16, K % 8 == 0.
 
     out is bfloat16 or float32 [M, N], or float32 [S, M, N] partial sums where S =
@@ -246,13 +247,14 @@ def gemm_tcgen05(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, status: to
     if out.dim() == 2:
         if S != 1:
             raise KernelError("a split product needs a float32 [S, M, N] output")
-        _want(out, "out", None, (M, N))
+        _want(out, "out", None, (M, N // 2 if epilogue == 1 else N))
     else:
         _want(out, "out", torch.float32, (S, M, N))
     lib = library()
     s_io = ctypes.c_int(S)
     check(lib, lib.sb_gemm_tcgen05(_ptr(out), _ptr(a), _ptr(w), M, N, K, _code(out.dtype),
-                                   ctypes.byref(s_io), _ptr(status), int(variant), _stream()), "gemm_tcgen05")
+                                   ctypes.byref(s_io), _ptr(status), int(variant), int(epilogue), _stream()),
+          "gemm_tcgen05")
     if s_io.value != S:
         raise KernelError(f"gemm_tcgen05 wrote {s_io.value} parts where {S} were expected")
     return S

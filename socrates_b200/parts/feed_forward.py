@@ -1,6 +1,10 @@
 """SwiGLU feed-forward: down(up(x) * silu(gate(x))), no bias
-(model/qwen/qwen_kv_cont.py:250-266).  gate and up are one matrix product here (the
-weights are concatenated when they are bound); silu(z) = z * sigmoid(z) in float32."""
+(model/qwen/qwen_kv_cont.py:250-266).  gate and up are one matrix product here: when the
+weights are bound their rows are interleaved (row 2f = gate_f, row 2f+1 = up_f), so that a
+gate and its up value are neighbours in the product's output.  For many rows the
+tensor-core kernel then applies SiLU*mul in its epilogue and the [N, 2F] intermediate is
+never written; otherwise a SiLU*mul kernel reads the interleaved product.
+silu(z) = z * sigmoid(z) in float32."""
 
 from __future__ import annotations
 
@@ -31,15 +35,18 @@ class SwiGLU(Part):
 
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype) -> None:
         n = self.name
-        self.gate_up = Linear(torch.cat([tensors[n + "gate_proj.weight"],
-                                         tensors[n + "up_proj.weight"]], dim=0))
+        gate, up = tensors[n + "gate_proj.weight"], tensors[n + "up_proj.weight"]
+        self.gate_up = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.inter, self.hidden))
         self.down = Linear(tensors[n + "down_proj.weight"])
 
     def forward(self, ctx, x: torch.Tensor) -> Branch:
         N = x.shape[0]
-        gu = self.gate_up(ctx, x, "gate_up")
-        act = ctx.buffers.take("act", N, (self.inter,), ctx.dtype)
-        ops.silu_mul(act, gu)
+        if ctx.can_fuse_silu_mul(N, self.gate_up.weight, x.dtype):
+            act = self.gate_up(ctx, x, "act", epilogue=1)
+        else:
+            gu = self.gate_up(ctx, x, "gate_up")
+            act = ctx.buffers.take("act", N, (self.inter,), ctx.dtype)
+            ops.silu_mul(act, gu, interleaved=True)
         return Branch(self.down(ctx, act, "branch", out="partial"))
 
 

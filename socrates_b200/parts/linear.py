@@ -20,13 +20,13 @@ class Linear:
         self.weight = weight.contiguous()
         self.out_features, self.in_features = weight.shape
 
-    def __call__(self, ctx, x: torch.Tensor, buffer: str, out: str = "model") -> torch.Tensor:
+    def __call__(self, ctx, x: torch.Tensor, buffer: str, out: str = "model", epilogue: int = 0) -> torch.Tensor:
         """`out`: "model" -> [M, N] in the model dtype; "float32" -> [M, N] float32;
         "partial" -> float32 [S, M, N]; "model_or_partial" -> partial sums when the
         product is cut along K (the weight-streaming regime), else the model dtype: for
         consumers that can add the parts themselves."""
         M = x.shape[0]
-        N = self.out_features
+        N = self.out_features // 2 if epilogue == 1 else self.out_features
         if out == "model_or_partial":
             out = "partial" if ctx.gemm_splits(M, self.weight, x.dtype) > 1 else "model"
         if out == "model":
@@ -38,5 +38,5 @@ class Linear:
             y = ctx.buffers.take_flat(buffer, S * M * N, torch.float32).view(S, M, N)
         else:
             raise ValueError(out)
-        ctx.gemm(y, x, self.weight)
+        ctx.gemm(y, x, self.weight, epilogue)
         return y

@@ -79,6 +79,43 @@ def test_gemm_tcgen05_one_hot_rows_and_columns(ops):
         assert torch.equal(out, w.float()[:, idx.to(DEV)].T.contiguous())
 
 
+@pytest.mark.parametrize("M,N,K", [(2048, 2560, 4096), (300, 19456, 256), (129, 6144, 320), (1000, 130, 64),
+                                   (70, 128, 72), (5000, 384, 96)])
+def test_gemm_tcgen05_persistent_many_tiles(ops, M, N, K):
+    """Shapes that give one block several tiles (two accumulators in turn), ragged edges,
+    and every tile width; compared with the one-tile-per-block kernel too."""
+    a, w, want = operands(M, N, K, seed=2)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_tcgen05(out, a, w, status)
+    close(out, want, K, False)
+    other = torch.empty_like(out)
+    ops.gemm_tcgen05(other, a, w, status, variant=4)
+    assert torch.equal(out, other)
+    outb = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tcgen05(outb, a, w, status)
+    close(outb, want, K, True)
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("M,F,K", [(200, 320, 96), (2048, 9728, 256), (65, 64, 64), (300, 203, 72)])
+def test_gemm_tcgen05_fused_silu_mul(ops, M, F, K):
+    """Interleaved gate/up rows: the epilogue writes up * silu(gate)."""
+    g = torch.Generator().manual_seed(M + F)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    gate = torch.randn(F, K, generator=g).to(torch.bfloat16).to(DEV)
+    up = torch.randn(F, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.stack([gate, up], dim=1).reshape(2 * F, K).contiguous()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tcgen05(out, a, w, status, epilogue=1)
+    gf, uf = a.double() @ gate.double().T, a.double() @ up.double().T
+    want = uf * gf * torch.sigmoid(gf)
+    err = float((out.double() - want).abs().max())
+    assert err <= 1e-4 * math.sqrt(K) * 8 + 2 ** -8 * float(want.abs().max()), err
+    assert int(status.item()) == 0
+
+
 def test_gemm_tcgen05_refuses(ops):
     from socrates_b200.kernels import KernelError
     status = torch.zeros(1, dtype=torch.int32, device=DEV)

@@ -82,12 +82,17 @@ def test_add_rmsnorm_selected_rows_leave_residual(ops, ref, dtype):
 
 # ---------------------------------------------------------------------------- silu * mul
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_silu_mul(ops, ref, dtype):
-    N, F = 13, 355
+@pytest.mark.parametrize("F", [355, 360, 96])
+def test_silu_mul(ops, ref, dtype, F):
+    N = 13
     gu = rand(N, 2 * F, dtype=dtype, scale=3.0)
     out = torch.empty(N, F, dtype=dtype, device=DEV)
     ops.silu_mul(out, gu)
     assert torch.allclose(out.float(), ref.silu_mul_ref(gu), **tol(dtype))
+    inter = torch.stack([gu[:, :F], gu[:, F:]], dim=2).reshape(N, 2 * F).contiguous()
+    out2 = torch.empty_like(out)
+    ops.silu_mul(out2, inter, interleaved=True)
+    assert torch.equal(out2, out)
 
 
 # ---------------------------------------------------------------------------- matrix product
