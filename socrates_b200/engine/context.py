@@ -148,12 +148,18 @@ class StepContext:
         """Causal attention of every token of the step over its row's pages.
 
         bfloat16 with a head size and group size the tensor-core kernels take: the
-        decode kernel when every request brings one token, else the tile kernel;
+        split-key decode kernel (mma.sync) when every request brings one token, else the
+        tile kernel: tcgen05 for head sizes 64 and 128, mma.sync for 16 and 32;
         everything else (the float32 engine above all) runs on the SIMT kernel.
         """
         Hkv, page_size, D = k_pool.shape[1], k_pool.shape[2], k_pool.shape[3]
         N = q.shape[0]
         tensor_cores = q.dtype == torch.bfloat16
+        if (tensor_cores and not self.all_decode and self.status is not None
+                and ops.attention_tcgen05_supports(num_heads, Hkv, D, page_size)):
+            ops.attention_prefill_tcgen05(out, q, k_pool, v_pool, table, self.seq_starts, self.seq_rows,
+                                          self.seq_first_pos, num_heads, scale, self.status, window)
+            return
         if tensor_cores and not self.all_decode and ops.attention_mma_supports(num_heads, Hkv, D, page_size, False):
             ops.attention_prefill_mma(out, q, k_pool, v_pool, table, self.seq_starts, self.seq_rows,
                                       self.seq_first_pos, num_heads, scale, window)

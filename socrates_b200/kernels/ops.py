@@ -328,3 +328,34 @@ def attention_decode_mma(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
 def attention_decode_mma_blocks_per_sm(head_dim: int, variant: int = 0) -> int:
     """Blocks of the decode attention kernel that are resident on one SM at a time."""
     return library().sb_attention_decode_mma_blocks_per_sm(int(head_dim), int(variant))
+
+
+def attention_tcgen05_supports(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 tile kernel takes this shape (bfloat16, head_dim 64 or 128)."""
+    return bool(library().sb_attention_tcgen05_supports(num_heads, num_kv_heads, head_dim, page_size))
+
+
+def attention_prefill_tcgen05(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                              block_table: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor,
+                              seq_first_pos: torch.Tensor, num_heads: int, scale: float, status: torch.Tensor,
+                              window: int = 0) -> None:
+    """Paged causal attention of prompt portions on tcgen05 (scores and P.V in tensor
+    memory, pages brought in by TMA).  Arguments as `attention_prefill_mma`, plus the int32
+    status word that receives a non-zero code if a bounded wait inside the kernel gave up."""
+    N = q.shape[0]
+    pages, Hkv, BS, D = k_pool.shape
+    R = seq_rows.numel()
+    _want(q, "q", torch.bfloat16, (N, num_heads * D))
+    _want(out, "out", torch.bfloat16, (N, num_heads * D))
+    _want(k_pool, "k_pool", torch.bfloat16)
+    _want(v_pool, "v_pool", torch.bfloat16, k_pool.shape)
+    _want(block_table, "block_table", torch.int32)
+    _want(seq_starts, "seq_starts", torch.int32, (R + 1,))
+    _want(seq_rows, "seq_rows", torch.int32, (R,))
+    _want(seq_first_pos, "seq_first_pos", torch.int32, (R,))
+    _want(status, "status", torch.int32)
+    lib = library()
+    check(lib, lib.sb_attention_prefill_tcgen05(
+        _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), pages, _ptr(block_table), block_table.shape[1],
+        _ptr(seq_starts), _ptr(seq_rows), _ptr(seq_first_pos), R, N, num_heads, Hkv, D, BS, int(window),
+        float(scale), _ptr(status), _stream()), "attention_prefill_tcgen05")
