@@ -327,7 +327,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
                    const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                    const int* __restrict__ block_table, int table_width, const int* __restrict__ token_rows,
                    const int* __restrict__ positions, int Hq, int Hkv, int BS, int window, float scale_log2,
-                   int NP) {
+                   int NP, int* __restrict__ counters) {
     sb::pdl_launch_dependents();     // the next kernel may begin its prologue
     sb::pdl_wait();                  // everything before this kernel is complete and visible
     constexpr int KTD = 16 * NW;                            // keys per tile
@@ -338,6 +338,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
     bf16* vbuf = kbuf + S * KTD * D;                        // S x [KTD][D]
     int* stab = reinterpret_cast<int*>(vbuf + S * KTD * D); // the pages of this partition: up to table_width
     __shared__ float w_m[NW][16], w_l[NW][16];
+    __shared__ int s_last;
 
     const int G = Hq / Hkv;
     const int bs_log2 = 31 - __clz(BS);                     // the page size is a power of two
@@ -355,14 +356,16 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
     const int k_end = min(hi, pg_end * BS);
     const int h0 = kh * G;
 
-    if (k_begin >= k_end) {                                 // an empty partition (only when NP > 1)
+    const bool empty = k_begin >= k_end;                    // an empty partition (only when NP > 1)
+    if (empty) {
         if (threadIdx.x < G) {
             float* ml = part_ml + (((size_t)n * Hq + h0 + threadIdx.x) * NP + part) * 2;
             ml[0] = -INFINITY;
             ml[1] = 0.f;
         }
-        return;
+        if (counters == nullptr) return;                    // the reduce kernel follows
     }
+    if (!empty) {
     const int tile_begin = k_begin / KTD, tile_end = (k_end + KTD - 1) / KTD;
     const int n_tiles = tile_end - tile_begin;
     for (int i = threadIdx.x; i < pg_end - pg_begin; i += NTHR) stab[i] = table[pg_begin + i];
@@ -446,10 +449,41 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
             part_o[(((size_t)n * Hq + h) * NP + part) * D + d] = o;
             if (d == 0) {
                 float* ml = part_ml + (((size_t)n * Hq + h) * NP + part) * 2;
-                ml[0] = M * scale_log2 / LOG2E;             // the reduce kernel works with natural exponents
+                ml[0] = M * scale_log2 / LOG2E;             // natural exponents, as the reduce kernel expects
                 ml[1] = L;
             }
         }
+    }
+    }   // !empty
+    if (NP == 1 || counters == nullptr) return;
+    // ---- the partition that finishes last merges all NP of them (no second launch):
+    //      out[h,:] = sum_p e^{m_p - M} o_p / sum_p e^{m_p - M} l_p over partitions with l > 0
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int prev = atomicAdd(&counters[n * Hkv + kh], 1);
+        s_last = prev == NP - 1;
+        if (s_last) counters[n * Hkv + kh] = 0;             // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < G * D; idx += NTHR) {
+        const int row = idx / D, d = idx - row * D;
+        const size_t slot = ((size_t)n * Hq + h0 + row) * NP;
+        float M = -INFINITY;
+        for (int p = 0; p < NP; ++p)
+            if (__ldcg(part_ml + (slot + p) * 2 + 1) > 0.f) M = fmaxf(M, __ldcg(part_ml + (slot + p) * 2));
+        float L = 0.f, o = 0.f;
+        for (int p = 0; p < NP; ++p) {
+            const float l = __ldcg(part_ml + (slot + p) * 2 + 1);
+            if (l > 0.f) {
+                const float f = expf(__ldcg(part_ml + (slot + p) * 2) - M);
+                L += f * l;
+                o += f * __ldcg(part_o + (slot + p) * D + d);
+            }
+        }
+        out[((size_t)n * Hq + h0 + row) * D + d] = __float2bfloat16_rn(o / L);
     }
 }
 
@@ -480,7 +514,7 @@ int launch_prefill(void* out, const void* q, const void* k_pool, const void* v_p
 template <int D, int NW, int S>
 int launch_decode_v(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool, const void* v_pool,
                     const int* block_table, int table_width, const int* token_rows, const int* positions, int N,
-                    int Hq, int Hkv, int BS, int window, float scale, int NP, cudaStream_t stream) {
+                    int Hq, int Hkv, int BS, int window, float scale, int NP, int* counters, cudaStream_t stream) {
     auto kernel = attn_decode_kernel<D, NW, S>;
     constexpr int smem = decode_smem<D, NW, S>();
     static bool configured = false;
@@ -493,8 +527,8 @@ int launch_decode_v(void* out, float* part_o, float* part_ml, const void* q, con
     dim3 grid(Hkv, N, NP);
     sb::launch(kernel, dim3(grid), dim3(32 * NW), smem + table_width * 4, stream, 
         (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
-        table_width, token_rows, positions, Hq, Hkv, BS, window, scale * LOG2E, NP);
-    if (NP > 1) {
+        table_width, token_rows, positions, Hq, Hkv, BS, window, scale * LOG2E, NP, counters);
+    if (NP > 1 && counters == nullptr) {
         dim3 rgrid(Hq, N);
         sb::launch(attn_reduce_kernel<bf16>, dim3(rgrid), dim3(128), 0, stream, (bf16*)out, part_o, part_ml, Hq, D, NP);
     }
@@ -509,9 +543,10 @@ constexpr int kVariantStages[kDecodeVariants] = {3, 2, 4, 6, 4};
 template <int D>
 int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool, const void* v_pool,
                   const int* block_table, int table_width, const int* token_rows, const int* positions, int N,
-                  int Hq, int Hkv, int BS, int window, float scale, int NP, cudaStream_t stream, int variant = 0) {
+                  int Hq, int Hkv, int BS, int window, float scale, int NP, cudaStream_t stream, int variant = 0,
+                  int* counters = nullptr) {
 #define SB_DEC(NW, S) launch_decode_v<D, NW, S>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, \
-                                                token_rows, positions, N, Hq, Hkv, BS, window, scale, NP, stream)
+                                                token_rows, positions, N, Hq, Hkv, BS, window, scale, NP, counters, stream)
     switch (variant) {
         case 1: return SB_DEC(4, 2);
         case 2: return SB_DEC(2, 4);
@@ -567,11 +602,14 @@ extern "C" int sb_attention_decode_mma_blocks_per_sm(int D, int variant) {
 
 // Steps in which every request brings one token.  Scratch as for sb_attention_simt.
 // `variant` selects (warps, stages) of the kernel; 0 is the default.
+// `counters`: null, or int32 [N * Hkv] that is zero before the first call (and is left zero):
+// then the partition of a (token, KV head) that finishes last merges the partitions itself
+// and no reduce kernel is launched.
 extern "C" int sb_attention_decode_mma(void* out, float* part_o, float* part_ml, const void* q,
                                        const void* k_pool, const void* v_pool, const int* block_table,
                                        int table_width, const int* token_rows, const int* positions, int N,
                                        int Hq, int Hkv, int D, int page_size, int window, float scale,
-                                       int num_partitions, int variant, cudaStream_t stream) {
+                                       int num_partitions, int variant, int* counters, cudaStream_t stream) {
     SB_REQUIRE(sb_attention_mma_supports(Hq, Hkv, D, page_size, 1),
                "attention_mma (decode): Hq=%d Hkv=%d head_dim=%d is not supported", Hq, Hkv, D);
     SB_REQUIRE(N > 0 && N <= 65535 && window >= 0 && table_width > 0, "attention_mma: bad sizes N=%d", N);
@@ -582,10 +620,10 @@ extern "C" int sb_attention_decode_mma(void* out, float* part_o, float* part_ml,
                "attention_mma: split over %d partitions needs scratch buffers", num_partitions);
     int rc;
     switch (D) {
-        case 16: rc = launch_decode<16>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant); break;
-        case 32: rc = launch_decode<32>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant); break;
-        case 64: rc = launch_decode<64>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant); break;
-        default: rc = launch_decode<128>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant); break;
+        case 16: rc = launch_decode<16>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant, counters); break;
+        case 32: rc = launch_decode<32>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant, counters); break;
+        case 64: rc = launch_decode<64>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant, counters); break;
+        default: rc = launch_decode<128>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant, counters); break;
     }
     if (rc != 0) return rc;
     SB_LAUNCH_CHECK();

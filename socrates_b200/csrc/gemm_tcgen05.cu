@@ -194,7 +194,7 @@ template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat
 // tma_b: the operand whose rows become accumulator columns, [rows_b, K], box {64, BN}.
 // SWAP = false: lanes are rows of C (m), columns are columns of C (n).
 // SWAP = true : lanes are columns of C (n), columns are rows of C (m).
-template <int BN, int STAGES, bool SWAP, typename TC>
+template <int BN, int STAGES, bool SWAP, typename TC, int EPI = 0>
 __global__ void __launch_bounds__(128)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     TC* __restrict__ C, int M, int N, int K, int kb_per_split, int* __restrict__ status) {
@@ -319,7 +319,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             uint32_t r[16];
             tmem_ld16(tmem_d + (static_cast<uint32_t>(warp * 32) << 16) + c0, r);
             tmem_ld_wait();
-            if (SWAP) {
+            if (SWAP && EPI == 1) {
+                // weight rows interleave gate and up: lane pairs (even = gate_f, odd = up_f);
+                // the even lane writes C[m, f] = up * silu(gate), C has N/2 columns
+                const int n = a0 + lane_row;
+                const int F = N >> 1;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float v = __uint_as_float(r[j]);
+                    const float up = __shfl_xor_sync(0xffffffffu, v, 1);
+                    const int m = b0 + c0 + j;
+                    if ((lane & 1) == 0 && n + 1 < N && m < M)
+                        store_out<TC>(C + (size_t)m * F + (n >> 1), up * (v / (1.0f + expf(-v))));
+                }
+            } else if (SWAP) {
                 const int n = a0 + lane_row;
                 if (n < N) {
 #pragma unroll
@@ -590,10 +603,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const 
 // ----------------------------------------------------------------------------- host side
 using sb::get_map;
 
-template <int BN, int STAGES, bool SWAP, typename TC>
+template <int BN, int STAGES, bool SWAP, typename TC, int EPI = 0>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, int K, dim3 grid, int kb_per_split,
            int* status, cudaStream_t stream) {
-    auto kernel = gemm_tcgen05_kernel<BN, STAGES, SWAP, TC>;
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, SWAP, TC, EPI>;
     constexpr int smem = STAGES * stage_bytes<BN>() + 1024;
     static bool configured = false;
     if (!configured) {
@@ -651,8 +664,8 @@ int dispatch(const void* A, const void* W, void* C, int M, int N, int K, int spl
     splits = (kb_total + kb_per_split - 1) / kb_per_split;      // no empty part
     *splits_out = splits;
     CUtensorMap ma, mb;
-    if (M <= 64 && epi != 0) {
-        sb_set_error("gemm_tcgen05: the fused SiLU*mul epilogue is for M > 64");
+    if (M <= 64 && epi != 0 && splits != 1) {
+        sb_set_error("gemm_tcgen05: the fused SiLU*mul epilogue cannot follow a K split");
         return SB_ERR_ARG;
     }
     if (M <= 64) {
@@ -669,6 +682,11 @@ int dispatch(const void* A, const void* W, void* C, int M, int N, int K, int spl
         // (qkv 7.6 vs 10.3 us, gate_up 19.1 vs 33.7 us), so it is the default; variant 2
         // selects the deep one.
         const bool deep = variant == 2;
+        if (epi == 1) {
+            if (bn == 16) return launch<16, 6, true, TC, 1>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
+            if (bn == 32) return launch<32, 5, true, TC, 1>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
+            return launch<64, 4, true, TC, 1>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
+        }
         if (bn == 16) return deep ? launch<16, 12, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream)
                                   : launch<16, 6, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
         if (bn == 32) return deep ? launch<32, 10, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream)
@@ -693,7 +711,7 @@ int dispatch(const void* A, const void* W, void* C, int M, int N, int K, int spl
         return launch_persistent<128, 6, TC, 0>(ma, mb, C, M, N, K, status, stream);
     }
     if (epi != 0) {
-        sb_set_error("gemm_tcgen05: the fused SiLU*mul epilogue needs M > 64, N >= 128 and no K split");
+        sb_set_error("gemm_tcgen05: the fused SiLU*mul epilogue needs N >= 128 and no K split");
         return SB_ERR_ARG;
     }
     // variant 4: the one-tile-per-block kernel also for many rows
@@ -718,7 +736,7 @@ int dispatch(const void* A, const void* W, void* C, int M, int N, int K, int spl
 //          2 = deep ring (one block per SM); 4 = one tile per block also for many rows
 //          (the default there is the persistent kernel).
 // epilogue: 0 = C[M,N]; 1 = W interleaves gate and up rows and C is [M, N/2] = up * silu(gate)
-//          (many rows, no K split).
+//          (no K split; for many rows N >= 128).
 extern "C" int sb_gemm_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, int c_dtype,
                                int* splits_io, int* status, int variant, int epilogue, cudaStream_t stream) {
     SB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);

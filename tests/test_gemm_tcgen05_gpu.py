@@ -98,7 +98,8 @@ def test_gemm_tcgen05_persistent_many_tiles(ops, M, N, K):
     assert int(status.item()) == 0
 
 
-@pytest.mark.parametrize("M,F,K", [(200, 320, 96), (2048, 9728, 256), (65, 64, 64), (300, 203, 72)])
+@pytest.mark.parametrize("M,F,K", [(200, 320, 96), (2048, 9728, 256), (65, 64, 64), (300, 203, 72),
+                                   (8, 9728, 2560), (1, 80, 64), (64, 203, 72), (17, 64, 96)])
 def test_gemm_tcgen05_fused_silu_mul(ops, M, F, K):
     """Interleaved gate/up rows: the epilogue writes up * silu(gate)."""
     g = torch.Generator().manual_seed(M + F)
