@@ -233,8 +233,9 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf
     const int bs_log2 = 31 - __clz(BS);                     // the page size is a power of two
     const int TQ = 64 / G;                                  // tokens per tile
     const int kh = blockIdx.y;
-    // ---- which request, which tile
-    int tile = blockIdx.x, r = 0, t0 = 0, n_tok = 0;
+    // ---- which request, which tile (reversed: later tiles of a prompt have more keys and
+    // should start first)
+    int tile = gridDim.x - 1 - blockIdx.x, r = 0, t0 = 0, n_tok = 0;
     for (; r < R; ++r) {
         const int a = seq_starts[r], len = seq_starts[r + 1] - a;
         const int tiles = (len + TQ - 1) / TQ;

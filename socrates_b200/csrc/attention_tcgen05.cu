@@ -12,9 +12,10 @@
 //   O += P V           tcgen05.mma with A = P from TMEM (hi, then lo on top) and B = V from
 //                      shared memory, MN-major (keys are the K dimension); O stays in TMEM.
 // The weights of tile i are written over the scores of tile i (same TMEM columns), there
-// are two such S/P buffers, and a fifth warp does nothing but issue copies and products:
-// QK(i+1) before the softmax warps have finished tile i, PV(i) as soon as they have, so the
-// tensor core works on tile i+1's scores and tile i-1's product during tile i's softmax.
+// are two such S/P buffers, a fifth warp does nothing but issue products and a sixth nothing
+// but issue the TMA copies (one box per lane): QK(i+1) goes out before the softmax warps have
+// finished tile i and PV(i) as soon as they have, so the tensor core works on tile i+1's
+// scores and tile i-1's product during tile i's softmax.
 // O is rescaled lazily: the exponent's reference maximum of a row only moves when the row
 // maximum grows by more than 2^8, and then the row of O in TMEM is multiplied once.
 // Tiles whose keys every row of the block may see skip the position masks.
@@ -177,7 +178,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-constexpr int THREADS = ROWS + 32;   // four softmax warps and the issuing warp
+constexpr int THREADS = ROWS + 64;   // four softmax warps, the MMA-issuing warp, the copy-issuing warp
 
 template <int D>
 __global__ void __launch_bounds__(THREADS)
@@ -192,12 +193,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
     constexpr int PANEL_KV = KTILE * 128;                  // bytes of one K or V panel
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t k_full[2], v_full[2];
-    __shared__ __align__(8) uint64_t s_full[2], p_ready[2], pv_full;
+    __shared__ __align__(8) uint64_t s_full[2], p_ready[2], v_free[2], pv_full;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const bool issuer = warp == 4;
+    const bool copier = warp == 5;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_s = base;
     const uint32_t k_s = q_s + q_bytes<D>();               // 2 buffers
@@ -216,6 +218,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
             mbar_init(smem_u32(&v_full[b]), 1);
             mbar_init(smem_u32(&s_full[b]), 1);
             mbar_init(smem_u32(&p_ready[b]), ROWS);
+            mbar_init(smem_u32(&v_free[b]), 1);
         }
         mbar_init(smem_u32(&pv_full), 1);
         abort_flag = 0;
@@ -229,8 +232,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
     sb::pdl_launch_dependents();
     sb::pdl_wait();                                        // q and the pages are written by earlier kernels
 
-    // ---- which request, which tile
-    int tile = blockIdx.x, r = 0, t0 = 0, n_tok = 0;
+    // ---- which request, which tile.  Blocks are handed out in launch order and later tiles of
+    // a prompt have more keys, so the order is reversed: the longest tiles start first and the
+    // short ones fill the tail.
+    int tile = gridDim.x - 1 - blockIdx.x, r = 0, t0 = 0, n_tok = 0;
     for (; r < R; ++r) {
         const int a = seq_starts[r], len = seq_starts[r + 1] - a;
         const int tiles = (len + TQ - 1) / TQ;
@@ -277,44 +282,68 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
     // position and starts at or after the last query's window start
     const int last_qlo = (window > 0 && hi > window) ? hi - window : 0;
 
-    if (issuer) {
-        // =============================================================== the issuing warp
+    if (copier) {
+        // =============================================================== the copy-issuing warp
+        // Tile t's keys go to K buffer t&1 once QK(t-2) has read it, its values to V buffer t&1
+        // once PV(t-2) has.  Each lane issues one box (page, panel); lane 0 arms the barrier.
+        if (active) {
+            const int lane = tid & 31;
+            const int pages = KTILE >> bs_log2;
+            const int n_ops = pages * PANELS;               // at most 8
+            bool ok = true;
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                const int b = t & 1;
+                const int pg = lane / PANELS, p = lane - pg * PANELS;
+                int y = 0;
+                if (lane < n_ops) {
+                    const int logical = (((tile_begin + t) * KTILE) >> bs_log2) + pg - table_base;
+                    const int phys = (logical >= 0 && logical < table_count) ? stab[logical] : 0;
+                    y = (phys * Hkv + kh) * BS;
+                }
+                const uint32_t off = b * kv_bytes<D>() + p * PANEL_KV + pg * BS * 128;
+                // ---- keys
+                if (t >= 2) {
+                    bool got = mbar_wait(smem_u32(&s_full[b]), ((t - 2) >> 1) & 1);
+                    got = __all_sync(0xffffffffu, got);
+                    if (!got) { ok = false; if (lane == 0) { atomicExch(status, 17); atomicExch(&abort_flag, 1); } break; }
+                }
+                if (lane == 0) mbar_arrive_expect_tx(smem_u32(&k_full[b]), kv_bytes<D>());
+                __syncwarp();
+                if (lane < n_ops) tma_load_2d(k_s + off, &tma_k, smem_u32(&k_full[b]), p * 64, y);
+                // ---- values
+                // (a barrier of its own per buffer: pv_full advances every tile and this warp runs
+                // two tiles ahead, so a parity wait on it could fall two phases behind)
+                if (t >= 2) {
+                    bool got = mbar_wait(smem_u32(&v_free[b]), ((t - 2) >> 1) & 1);
+                    got = __all_sync(0xffffffffu, got);
+                    if (!got) { ok = false; if (lane == 0) { atomicExch(status, 18); atomicExch(&abort_flag, 1); } break; }
+                }
+                if (lane == 0) mbar_arrive_expect_tx(smem_u32(&v_full[b]), kv_bytes<D>());
+                __syncwarp();
+                if (lane < n_ops) tma_load_2d(v_s + off, &tma_v, smem_u32(&v_full[b]), p * 64, y);
+            }
+        }
+    } else if (issuer) {
+        // =============================================================== the MMA-issuing warp
         if (active && (tid & 31) == 0) {
             bool ok = true;
-            auto load_tile = [&](int t, int b, int which) {
-                const uint32_t bar = smem_u32(which ? &v_full[b] : &k_full[b]);
-                mbar_arrive_expect_tx(bar, kv_bytes<D>());
-                const int pages = KTILE >> bs_log2;
-                for (int pg = 0; pg < pages; ++pg) {
-                    const int logical = ((t * KTILE) >> bs_log2) + pg - table_base;
-                    const int phys = (logical >= 0 && logical < table_count) ? stab[logical] : 0;
-                    const int y = (phys * Hkv + kh) * BS;
-#pragma unroll
-                    for (int p = 0; p < PANELS; ++p) {
-                        const uint32_t off = b * kv_bytes<D>() + p * PANEL_KV + pg * BS * 128;
-                        if (which) tma_load_2d(v_s + off, &tma_v, bar, p * 64, y);
-                        else tma_load_2d(k_s + off, &tma_k, bar, p * 64, y);
-                    }
-                }
-            };
             constexpr uint32_t idesc_qk = make_idesc(KTILE, false);
             constexpr uint32_t idesc_pv = make_idesc(D, true);
+            const uint64_t dq = desc_kmajor(q_s), dk = desc_kmajor(k_s);
+            const uint64_t dv = desc_mnmajor(v_s, PANEL_KV >> 4);
             auto issue_qk = [&](int b) {
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t pq = (kk >> 2) * PANEL_Q + (kk & 3) * 32;
-                    const uint32_t pk = b * kv_bytes<D>() + (kk >> 2) * PANEL_KV + (kk & 3) * 32;
-                    mma_ss(tmem + COL_SP + 64 * b, desc_kmajor(q_s + pq), desc_kmajor(k_s + pk), idesc_qk,
-                           kk > 0 ? 1u : 0u);
+                    // the start address sits in the low bits of a descriptor in units of 16 bytes
+                    const uint32_t pq = ((kk >> 2) * PANEL_Q + (kk & 3) * 32) >> 4;
+                    const uint32_t pk = (b * kv_bytes<D>() + (kk >> 2) * PANEL_KV + (kk & 3) * 32) >> 4;
+                    mma_ss(tmem + COL_SP + 64 * b, dq + pq, dk + pk, idesc_qk, kk > 0 ? 1u : 0u);
                 }
                 tc_commit(smem_u32(&s_full[b]));
             };
             auto fail = [&](int code) { ok = false; atomicExch(status, code); atomicExch(&abort_flag, 1); };
 
-            load_tile(tile_begin, 0, 0);
-            load_tile(tile_begin, 0, 1);
-            if (n_tiles > 1) load_tile(tile_begin + 1, 1, 0);
             if (!mbar_wait(smem_u32(&k_full[0]), 0)) fail(11);
             if (ok) issue_qk(0);
             for (int i = 0; i < n_tiles && ok; ++i) {
@@ -329,34 +358,20 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
                     if (i > 0 && !mbar_wait(smem_u32(&pv_full), (i - 1) & 1)) { fail(13); break; }
                     issue_qk(b ^ 1);
                 }
-                // QK(i) has read K buffer b: refill it with tile i+2
-                if (!mbar_wait(smem_u32(&s_full[b]), (i >> 1) & 1)) { fail(12); break; }
-                if (i + 2 < n_tiles) load_tile(tile_begin + i + 2, b, 0);
                 // the softmax warps have written P(i) (and zeroed unseen V rows); V(i) has landed
                 if (!mbar_wait(smem_u32(&p_ready[b]), (i >> 1) & 1)) { fail(16); break; }
                 if (!mbar_wait(smem_u32(&v_full[b]), (i >> 1) & 1)) { fail(14); break; }
-                // (V buffer b^1, refilled below, was last read by PV(i-1): complete, see above.)
                 tc_fence_after();
                 const uint32_t pbase = tmem + COL_SP + 64 * b;
 #pragma unroll
-                for (int j = 0; j < KTILE / 16; ++j) {
-                    const uint64_t dv = desc_mnmajor(v_s + b * kv_bytes<D>() + j * 2048, PANEL_KV >> 4);
-                    mma_ts(tmem + COL_O, pbase + j * 8, dv, idesc_pv, (i > 0 || j > 0) ? 1u : 0u);
-                }
+                for (int j = 0; j < KTILE / 16; ++j)
+                    mma_ts(tmem + COL_O, pbase + j * 8, dv + ((b * kv_bytes<D>() + j * 2048) >> 4), idesc_pv,
+                           (i > 0 || j > 0) ? 1u : 0u);
 #pragma unroll
-                for (int j = 0; j < KTILE / 16; ++j) {
-                    const uint64_t dv = desc_mnmajor(v_s + b * kv_bytes<D>() + j * 2048, PANEL_KV >> 4);
-                    mma_ts(tmem + COL_O, pbase + 32 + j * 8, dv, idesc_pv, 1u);
-                }
+                for (int j = 0; j < KTILE / 16; ++j)
+                    mma_ts(tmem + COL_O, pbase + 32 + j * 8, dv + ((b * kv_bytes<D>() + j * 2048) >> 4), idesc_pv, 1u);
                 tc_commit(smem_u32(&pv_full));
-                if (i + 1 < n_tiles) load_tile(tile_begin + i + 1, b ^ 1, 1);
-            }
-            if (!ok) {
-                // a wait gave up: let copies in flight land (bounded) before the block exits
-                for (int b = 0; b < 2; ++b) {
-                    mbar_wait(smem_u32(&k_full[b]), 0);
-                    mbar_wait(smem_u32(&v_full[b]), 0);
-                }
+                tc_commit(smem_u32(&v_free[b]));            // V buffer b may be refilled
             }
         }
     } else if (active) {
@@ -517,6 +532,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
                     }
                 }
             }
+        }
+    }
+    if (tid == 0 && *((volatile int*)&abort_flag)) {
+        // a wait gave up: let copies in flight land (bounded) before the block exits
+        for (int b = 0; b < 2; ++b) {
+            mbar_wait(smem_u32(&k_full[b]), 0);
+            mbar_wait(smem_u32(&v_full[b]), 0);
         }
     }
     tc_fence_before();
