@@ -68,9 +68,11 @@ class ClockSampler:
         self.proc, self.lines, self.index = None, [], index
 
     def start(self):
+        if os.environ.get("BENCH_NO_CLOCKS") == "1":      # to see what the sampling itself costs
+            return
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -164,9 +166,9 @@ def main():
 
     model = build_random_model(config, 0, torch.bfloat16, dev)
     rows_needed = max(B, 1 if args.skip_points else 64)
-    pages_per_row = -(-(ctx + 2 * (K + W) + 64) // page)
+    pages_per_row = -(-(ctx + 2 * (K + W) + rows_needed + 96) // page)
     engine = Engine(model, device="cuda:0", dtype="bfloat16", compile=True, max_batch=rows_needed,
-                    max_len=max_len, max_new_tokens=K + W + 8, block_size=page,
+                    max_len=max_len, max_new_tokens=K + W + rows_needed + 32, block_size=page,
                     num_blocks=rows_needed * pages_per_row + 8, token_budget=max(2048, rows_needed))
     cache, runner = engine.cache, engine.runner
     for g in cache.groups:                      # live KV: any finite values, the bytes are what is timed
@@ -247,8 +249,10 @@ def main():
         # Through the entry point: B requests with ctx-token prompts are prefilled by the
         # scheduler, then K decode steps are timed; each step copies its inputs from pinned
         # host memory and reads its sampled tokens back to the host.
+        # (prompts are prefilled one a step, so the first request is B tokens ahead of the last:
+        # room for that, so that nobody finishes inside the timed region)
         prompts = torch.randint(1, V, (B, ctx), generator=gen).tolist()
-        reqs = [engine.submit(p, max_new_tokens=K + W + 4) for p in prompts]
+        reqs = [engine.submit(p, max_new_tokens=K + W + B + 16) for p in prompts]
         while any(r.cached < ctx for r in reqs):
             engine.step()
         for _ in range(W):
@@ -261,6 +265,7 @@ def main():
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
         made = sum(len(r.output) for r in reqs) - done_before
+        assert made == B * K, "a request finished inside the timed region"
         for r in reqs:
             r.cancelled = True
         engine.scheduler.sweep()

@@ -72,6 +72,7 @@ class PageGroup:
         # Logical block -> page for each row; 0 where nothing is held (never written,
         # or given back after the window passed).
         self.row_pages: List[List[int]] = [[] for _ in range(max_rows)]
+        self.freed_upto: List[int] = [0] * max_rows     # blocks below this were given back (window)
         self.dirty: set[int] = set()
 
     def slot_of(self, entry: int) -> int:
@@ -145,17 +146,17 @@ class CacheManager:
             t[row].zero_()
 
     def pages_needed(self, row: int, new_len: int) -> List[int]:
-        """Pages each group still lacks for the row to hold `new_len` tokens."""
+        """Pages each group still lacks for the row to hold `new_len` tokens.
+
+        A row's pages are taken in order and given back only from the front (behind a
+        window), so the blocks it lacks are exactly those past the end of its list, from
+        the first block a later query can still see.
+        """
+        last = pages_for(new_len, self.page_size)              # exclusive
         out = []
         for g in self.groups:
-            have = g.row_pages[row]
             first = g.first_needed_block(self.lengths[row])
-            last = pages_for(new_len, self.page_size)          # exclusive
-            need = 0
-            for b in range(first, last):
-                if b >= len(have) or have[b] == 0:
-                    need += 1
-            out.append(need)
+            out.append(max(0, last - max(first, len(g.row_pages[row]))))
         return out
 
     def can_reserve(self, row: int, new_len: int) -> bool:
@@ -173,21 +174,22 @@ class CacheManager:
             raise ValueError(f"row {row} is not in use")
         if new_len > self.max_len:
             raise ValueError(f"{new_len} tokens exceed the row limit of {self.max_len}")
-        if not self.can_reserve(row, new_len):
+        needs = self.pages_needed(row, new_len)
+        if any(n > g.allocator.n_free for n, g in zip(needs, self.groups)):
             return False
         last = pages_for(new_len, self.page_size)
-        for g in self.groups:
+        for g, need in zip(self.groups, needs):
+            if need == 0:
+                continue
             have = g.row_pages[row]
             first = g.first_needed_block(self.lengths[row])
-            while len(have) < last:
+            while len(have) < min(first, last):                 # blocks no query will see again
                 have.append(0)
-            missing = [b for b in range(first, last) if have[b] == 0]
-            if missing:
-                pages = g.allocator.alloc(len(missing))
-                for b, p in zip(missing, pages):
-                    have[b] = p
-                    g.host_table[row, b] = p
-                g.dirty.add(row)
+            pages = g.allocator.alloc(need)
+            start = len(have)
+            have.extend(pages)
+            g.host_table[row, start:start + need] = torch.tensor(pages, dtype=torch.int32)
+            g.dirty.add(row)
         return True
 
     def commit(self, row: int, new_len: int) -> None:
@@ -200,7 +202,9 @@ class CacheManager:
                 continue
             keep_from = g.first_needed_block(new_len)
             have = g.row_pages[row]
-            gone = [b for b in range(min(keep_from, len(have))) if have[b] != 0]
+            upto = min(keep_from, len(have))
+            gone = [b for b in range(g.freed_upto[row], upto) if have[b] != 0]
+            g.freed_upto[row] = max(g.freed_upto[row], upto)
             if gone:
                 g.allocator.free([have[b] for b in gone])
                 for b in gone:
@@ -220,6 +224,7 @@ class CacheManager:
                 g.host_table[row].zero_()
                 g.dirty.add(row)
             g.row_pages[row] = []
+            g.freed_upto[row] = 0
         self.lengths[row] = 0
         self.active[row] = False
 
@@ -234,6 +239,7 @@ class CacheManager:
             raise ValueError(f"row {dst} is still in use; release it first")
         for g in self.groups:
             g.row_pages[dst], g.row_pages[src] = g.row_pages[src], []
+            g.freed_upto[dst], g.freed_upto[src] = g.freed_upto[src], 0
             g.host_table[dst].copy_(g.host_table[src])
             g.host_table[src].zero_()
             g.dirty.update((src, dst))

@@ -130,8 +130,10 @@ class Engine:
                    for e in plan.entries]
         args = [SamplingArgs(t, s, c) for (t, s, c) in self.scheduler.sampling_args(plan)]
         result = self.runner.step(entries, args)
-        tokens = result.tokens.tolist() if result.tokens is not None else []   # the step's read-back
-        self.runner.check_status()
+        # the step's one read-back: sampled tokens and the kernels' status word together
+        tokens = self.runner.read_tokens(len(args)) if result.tokens is not None else []
+        if result.tokens is None:
+            self.runner.check_status()
         self.scheduler.complete(plan, tokens)
         self.steps += 1
         return True

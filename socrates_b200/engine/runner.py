@@ -77,9 +77,15 @@ class ModelRunner:
         self.dev_meta = torch.zeros(self.layout.total, dtype=torch.int32, device=self.device)
         self._staging = [[torch.zeros(self.layout.total, dtype=torch.int32).pin_memory(), None]
                          for _ in range(4)]
+        self._staging_np = [b.numpy() for b, _ in self._staging]
+        self._staging_f32 = [b.view(torch.float32).numpy() for b, _ in self._staging]
         self._next = 0
-        self.sampled = torch.zeros(max_tokens, dtype=torch.int32, device=self.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # sampled tokens and the kernels' status word share one buffer, so that a step's
+        # read-back is one copy: [status, token 0, token 1, ...]
+        self._readback = torch.zeros(max_tokens + 1, dtype=torch.int32, device=self.device)
+        self.status = self._readback[0:1]
+        self.sampled = self._readback[1:]
+        self._events = [torch.cuda.Event() for _ in self._staging]
         self.sample_scratch = torch.zeros(ops.sample_scratch_size(max_tokens, self.vocab), dtype=torch.int32,
                                           device=self.device)
         self.use_graphs = use_graphs and model.supports_graph
@@ -149,22 +155,21 @@ class ModelRunner:
             raise ValueError(f"{len(sampling)} sampling entries for {M} wanted logits")
 
         buf, slot = self._stage()
-        buf[L.ids:L.ids + N] = torch.tensor(ids, dtype=torch.int32)
-        buf[L.pos:L.pos + N] = torch.tensor(pos, dtype=torch.int32)
-        buf[L.rows:L.rows + N] = torch.tensor(rows, dtype=torch.int32)
+        nb = self._staging_np[slot]                 # numpy view of the pinned buffer: cheap list assignment
+        nb[L.ids:L.ids + N] = ids
+        nb[L.pos:L.pos + N] = pos
+        nb[L.rows:L.rows + N] = rows
         if M:
-            buf[L.logit:L.logit + M] = torch.tensor(logit, dtype=torch.int32)
+            nb[L.logit:L.logit + M] = logit
         if sampling is not None and M:
-            buf[L.temp:L.temp + M] = torch.tensor([s.temperature for s in sampling],
-                                                  dtype=torch.float32).view(torch.int32)
-            buf[L.seed:L.seed + M] = torch.tensor([_as_i32(s.seed) for s in sampling], dtype=torch.int32)
-            buf[L.counter:L.counter + M] = torch.tensor([_as_i32(s.counter) for s in sampling],
-                                                        dtype=torch.int32)
-        buf[L.seq_starts:L.seq_starts + R + 1] = torch.tensor(starts, dtype=torch.int32)
-        buf[L.seq_rows:L.seq_rows + R] = torch.tensor([e.row for e in entries], dtype=torch.int32)
-        buf[L.seq_first:L.seq_first + R] = torch.tensor([e.start for e in entries], dtype=torch.int32)
-        self.dev_meta.copy_(buf, non_blocking=True)
-        ev = torch.cuda.Event()
+            self._staging_f32[slot][L.temp:L.temp + M] = [s.temperature for s in sampling]
+            nb[L.seed:L.seed + M] = [_as_i32(s.seed) for s in sampling]
+            nb[L.counter:L.counter + M] = [_as_i32(s.counter) for s in sampling]
+        nb[L.seq_starts:L.seq_starts + R + 1] = starts
+        nb[L.seq_rows:L.seq_rows + R] = [e.row for e in entries]
+        nb[L.seq_first:L.seq_first + R] = [e.start for e in entries]
+        self.dev_meta.copy_(buf, non_blocking=True)     # the step's one host-to-device copy
+        ev = self._events[slot]
         ev.record()
         self._staging[slot][1] = ev
         return N, M, R, all_decode, max_ctx
@@ -179,6 +184,16 @@ class ModelRunner:
             logit_index=m[L.logit:L.logit + M] if M else None,
             all_decode=all_decode, max_context=max_ctx, host_batch=host_batch, num_sms=self.num_sms,
             status=self.status)
+
+    def read_tokens(self, count: int) -> List[int]:
+        """The `count` tokens the last step sampled, as a host list, and a check of the
+        kernels' status word, in ONE device-to-host copy (which also waits for the step)."""
+        host = self._readback[:count + 1].tolist()
+        if host[0] != 0:
+            self.status.zero_()
+            raise RuntimeError(f"a tensor-core kernel gave up waiting on its pipeline (code {host[0]}); "
+                               f"the step's results are not valid")
+        return host[1:]
 
     def check_status(self) -> None:
         """Raise if a kernel reported that one of its bounded waits gave up.  Reads one
