@@ -60,7 +60,7 @@ class Engine:
     def __init__(self, model, tok=None, device: str = "cuda:0", dtype="bfloat16",
                  compile: bool = True, max_batch: int = 64, max_len: int = 8192,
                  max_new_tokens: int = 1024, block_size: int = 16, num_blocks: Optional[int] = None,
-                 token_budget: int = 2048, max_queue: Optional[int] = None):
+                 token_budget: int = 2048, max_queue: Optional[int] = None, warmup: bool = False):
         if not torch.cuda.is_available():
             raise RuntimeError("socrates_b200.Engine needs a CUDA device; there is no CPU path")
         require_kernels()                      # fail at start-up, not on the first step
@@ -92,6 +92,18 @@ class Engine:
         self.scheduler = Scheduler(self.cache, max_batch, max_len, self.config.token_budget,
                                    self.config.queue_limit, stop)
         self.steps = 0
+        if warmup:
+            self.warmup()
+
+    def warmup(self) -> None:
+        """Record one decode graph per batch width now instead of at the first step of each
+        width (the reference warms all its widths in its constructor,
+        model/inference_paged.py:110-130)."""
+        t0 = time.perf_counter()
+        n = self.runner.warmup(self.max_batch)
+        if n:
+            print(f"paged decode graphs warm for 1..{self.max_batch} rows in {time.perf_counter() - t0:.1f}s",
+                  flush=True)
 
     # ------------------------------------------------------------------ requests
     def submit(self, prompt: Union[str, Sequence[int]], max_new_tokens: Optional[int] = None,

@@ -195,6 +195,43 @@ class ModelRunner:
                                f"the step's results are not valid")
         return host[1:]
 
+    @torch.no_grad()
+    def warmup(self, max_width: int, sample: bool = True) -> int:
+        """Record the decode graph of every batch width 1..max_width before serving, as the
+        reference does at start-up (model/inference_paged.py:110-130).  The steps run on rows
+        that own no page, so everything they write lands in the null page.  Returns the
+        number of graphs recorded."""
+        if not self.use_graphs:
+            return 0
+        L, made = self.layout, 0
+        for n in range(1, min(max_width, self.max_seqs, self.cache.max_rows) + 1):
+            key = (n, sample)
+            if key in self._graphs:
+                continue
+            buf, slot = self._stage()
+            nb = self._staging_np[slot]
+            nb[:] = 0
+            nb[L.rows:L.rows + n] = list(range(n))
+            nb[L.logit:L.logit + n] = list(range(n))
+            nb[L.seq_starts:L.seq_starts + n + 1] = list(range(n + 1))
+            nb[L.seq_rows:L.seq_rows + n] = list(range(n))
+            self.dev_meta.copy_(buf, non_blocking=True)
+            ev = self._events[slot]
+            ev.record()
+            self._staging[slot][1] = ev
+            ctx = self._context(n, n, n, True, self.cache.max_len, None)
+            self._run(ctx, n, sample)                       # loads every kernel, sizes every buffer
+            graph = torch.cuda.CUDAGraph()
+            before = Counters.launches
+            with torch.cuda.graph(graph):
+                logits, tokens = self._run(ctx, n, sample)
+            self._graph_kernels[key] = Counters.launches - before
+            self._graphs[key] = (graph, logits, tokens)
+            self._eager_decode_done.add(key)
+            made += 1
+        torch.cuda.synchronize()
+        return made
+
     def check_status(self) -> None:
         """Raise if a kernel reported that one of its bounded waits gave up.  Reads one
         word back, so call it where the host synchronises anyway (after a step's tokens

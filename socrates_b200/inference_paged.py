@@ -57,6 +57,8 @@ def main(argv=None) -> int:
     ap.add_argument("--token-budget", type=int, default=2048, help="most tokens one step runs")
     ap.add_argument("--temperature", type=float, default=0.0, help="0 = greedy")
     ap.add_argument("--no-compile", action="store_true", help="no CUDA graphs (same as COMPILE=0)")
+    ap.add_argument("--no-warmup", action="store_true",
+                    help="record each decode graph at the first step of its width instead of at start-up")
     ap.add_argument("--prompt", action="append", default=[], help="a text prompt (byte tokenizer); repeatable")
     ap.add_argument("--prompt-ids", action="append", default=[], help="a prompt as comma-separated token ids; repeatable")
     ap.add_argument("--num-prompts", type=int, default=0, help="this many random prompts")
@@ -88,7 +90,8 @@ def main(argv=None) -> int:
     compile_ = _env_flag("COMPILE") and not args.no_compile
     engine = Engine(model_dir, tok=tok, device=args.device, dtype=args.dtype, compile=compile_,
                     max_batch=args.max_batch, max_len=args.max_len, max_new_tokens=args.max_new_tokens,
-                    block_size=args.block_size, num_blocks=args.num_blocks, token_budget=args.token_budget)
+                    block_size=args.block_size, num_blocks=args.num_blocks, token_budget=args.token_budget,
+                    warmup=not args.no_warmup)
 
     prompts = list(args.prompt)
     prompts += [[int(t) for t in p.split(",") if t.strip()] for p in args.prompt_ids]

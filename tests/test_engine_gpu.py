@@ -138,6 +138,35 @@ def test_first_tokens_of_a_sequence(tmp_path):
     assert float((l12 - ref[1:]).abs().max()) / scale < 1e-4
 
 
+def test_warmup_records_every_width_and_changes_nothing(tmp_path):
+    folder = make_folder(tmp_path, "B")
+    ps = prompts_for("B", [9, 30, 2, 17])
+    cold = engine_for(folder, "bfloat16").generate(ps, max_new_tokens=12)
+    eng = engine_for(folder, "bfloat16", warmup=True)
+    assert len(eng.runner._graphs) == 4                     # widths 1..max_batch
+    replays = eng.runner.graph_replays
+    assert eng.generate(ps, max_new_tokens=12) == cold
+    assert eng.runner.graph_replays > replays
+    assert len(eng.runner._graphs) == 4                     # nothing was recorded while serving
+
+
+def test_command_line(tmp_path):
+    import json
+    import subprocess
+    import sys
+    from tiny_configs import TINY_A
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(TINY_A))
+    root = __import__("pathlib").Path(__file__).resolve().parent.parent
+    proc = subprocess.run([sys.executable, "-m", "socrates_b200.inference_paged", "--random-config", str(cfg),
+                           "--num-prompts", "3", "--prompt-len", "9", "--max-new-tokens", "5", "--max-len", "64",
+                           "--max-batch", "2", "--prompt", "hello"], cwd=str(root), capture_output=True, text=True,
+                          timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert "4 requests, 2 rows" in proc.stdout and "tok/s" in proc.stdout.splitlines()[-1]
+    assert "> hello" in proc.stdout
+
+
 def test_entry_point_guards(tmp_path):
     from socrates_b200 import Engine, TooLong
     folder = make_folder(tmp_path, "A")
