@@ -60,6 +60,11 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -127,7 +132,7 @@ template <int D> struct RowState {
 template <int D, int NK>
 __device__ __forceinline__ void warp_tile(RowState<D>& st, const uint32_t (&qf)[D / 16][4], const bf16* ks,
                                           const bf16* vs, int kb, int tile_start, const int (&qpos)[2],
-                                          const int (&qlo)[2], int klo, int khi, float scale_log2) {
+                                          const int (&qlo)[2], int klo, int khi, float scale_log2, bool masked) {
     const int lane = threadIdx.x & 31;
     float s[NK / 8][4];
 #pragma unroll
@@ -146,52 +151,65 @@ __device__ __forceinline__ void warp_tile(RowState<D>& st, const uint32_t (&qf)[
             mma_bf16(s[2 * nb2 + 1], qf[kk], r[2], r[3]);
         }
     }
-    // ---- mask and row maxima
+    // ---- mask (only where some key of these NK may be invisible to some row) and row maxima
     float mx[2] = {-INFINITY, -INFINITY};
+    if (masked) {
 #pragma unroll
-    for (int nb = 0; nb < NK / 8; ++nb) {
+        for (int nb = 0; nb < NK / 8; ++nb) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int kpos = tile_start + kb + nb * 8 + 2 * (lane & 3) + (e & 1);
-            const int r = e >> 1;
-            const bool keep = kpos <= qpos[r] && kpos >= qlo[r] && kpos >= klo && kpos < khi;
-            s[nb][e] = keep ? s[nb][e] : -INFINITY;
-            mx[r] = fmaxf(mx[r], s[nb][e]);
+            for (int e = 0; e < 4; ++e) {
+                const int kpos = tile_start + kb + nb * 8 + 2 * (lane & 3) + (e & 1);
+                const int r = e >> 1;
+                const bool keep = kpos <= qpos[r] && kpos >= qlo[r] && kpos >= klo && kpos < khi;
+                s[nb][e] = keep ? s[nb][e] : -INFINITY;
+            }
         }
     }
-    float alpha[2], m_use[2];
+#pragma unroll
+    for (int nb = 0; nb < NK / 8; ++nb) {
+        mx[0] = fmaxf(mx[0], fmaxf(s[nb][0], s[nb][1]));
+        mx[1] = fmaxf(mx[1], fmaxf(s[nb][2], s[nb][3]));
+    }
+    // The exponent's reference st.m[r] of a row moves only when the row maximum outgrew it by
+    // more than 2^8 (weights then stay below 2^8, far inside float32 and bfloat16 range), so
+    // most tiles rescale nothing.
+    float neg_m[2];
+    bool any_grow = false;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-        const float m_new = fmaxf(st.m[r], mx[r]);
-        m_use[r] = m_new == -INFINITY ? 0.f : m_new;
-        alpha[r] = exp2f((st.m[r] - m_use[r]) * scale_log2);      // m == -inf gives 0
-        st.m[r] = m_new;
-        st.l[r] *= alpha[r];
+        const bool grow = mx[r] > -INFINITY && (st.m[r] == -INFINITY || (mx[r] - st.m[r]) * scale_log2 > 8.0f);
+        if (grow) {
+            const float alpha = st.m[r] == -INFINITY ? 0.f : exp2f((st.m[r] - mx[r]) * scale_log2);
+            st.m[r] = mx[r];
+            st.l[r] *= alpha;
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) {
+                st.o[i][2 * r] *= alpha;
+                st.o[i][2 * r + 1] *= alpha;
+            }
+        }
+        any_grow |= grow;
+        neg_m[r] = st.m[r] == -INFINITY ? 0.f : -st.m[r] * scale_log2;
     }
-    // ---- P = exp2(S - m) in float32.  For the product with V each weight is split into
-    // two bfloat16 terms, p = hi + lo (16 bits of mantissa together), so that the
-    // softmax weights are not cut to 8 bits before they are used.
+    (void)any_grow;
+    // ---- P = 2^(S*scale - m*scale) in float32 (one multiply-add, one ex2; masked scores
+    // are -inf and give 0).  For the product with V each weight is split into two bfloat16
+    // terms, p = hi + lo (16 bits of mantissa together), so that the softmax weights are not
+    // cut to 8 bits before they are used.
     uint32_t pk_hi[NK / 8][2], pk_lo[NK / 8][2];
 #pragma unroll
     for (int nb = 0; nb < NK / 8; ++nb) {
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-            const float p0 = exp2f((s[nb][2 * r] - m_use[r]) * scale_log2);      // masked: exp2(-inf) = 0
-            const float p1 = exp2f((s[nb][2 * r + 1] - m_use[r]) * scale_log2);
+            const float p0 = ex2_approx(fmaf(s[nb][2 * r], scale_log2, neg_m[r]));
+            const float p1 = ex2_approx(fmaf(s[nb][2 * r + 1], scale_log2, neg_m[r]));
             st.l[r] += p0 + p1;
             const uint32_t hi = pack_bf16(p0, p1);
             pk_hi[nb][r] = hi;
             pk_lo[nb][r] = pack_bf16(p0 - __uint_as_float(hi << 16), p1 - __uint_as_float(hi & 0xffff0000u));
         }
-    }
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-        st.o[i][0] *= alpha[0];
-        st.o[i][1] *= alpha[0];
-        st.o[i][2] *= alpha[1];
-        st.o[i][3] *= alpha[1];
     }
     // ---- O += P V
 #pragma unroll
@@ -252,6 +270,7 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf
     const int hi = first_pos + n_tok;                       // keys [lo, hi) are needed by this tile
     const int lo = (window > 0 && first_pos + 1 > window) ? first_pos + 1 - window : 0;
     const int tile_begin = lo / KT, tile_end = (hi + KT - 1) / KT;
+    const int last_qlo = (window > 0 && hi > window) ? hi - window : 0;
     const int table_base = lo / BS;
     for (int i = threadIdx.x; i <= (hi - 1) / BS - table_base; i += THREADS) stab[i] = table[table_base + i];
     __syncthreads();
@@ -298,8 +317,12 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf
             for (int kk = 0; kk < D / 16; ++kk)
                 ldmatrix_x4(qf[kk], smem_u32(qs + tile_off<D>(warp * 16 + (lane & 15), kk * 2 + (lane >> 4))));
         }
-        warp_tile<D, KT>(st, qf, kbuf + buf * KT * D, vbuf + buf * KT * D, 0, (tile_begin + i) * KT, qpos, qlo, lo,
-                         hi, scale_log2);
+        // every row of the block sees every key of a tile that ends at or before the first query
+        // and starts at or after the last query's window start; other tiles need the masks
+        const int ts = (tile_begin + i) * KT;
+        const bool masked = ts + KT - 1 > first_pos || ts < last_qlo || n_tok < TQ;
+        warp_tile<D, KT>(st, qf, kbuf + buf * KT * D, vbuf + buf * KT * D, 0, ts, qpos, qlo, lo, hi, scale_log2,
+                         masked);
         __syncthreads();
     }
     // ---- write
@@ -406,8 +429,10 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         }
         // warp w takes keys 16w .. 16w+15 of the tile
         const int buf = i % S;
-        warp_tile<D, 16>(st, qf, kbuf + buf * KTD * D, vbuf + buf * KTD * D, warp * 16, (tile_begin + i) * KTD,
-                         qpos, qlo, k_begin, k_end, scale_log2);
+        const int ts = (tile_begin + i) * KTD;
+        const bool masked = ts < k_begin || ts + KTD > k_end;       // only the partition's edge tiles
+        warp_tile<D, 16>(st, qf, kbuf + buf * KTD * D, vbuf + buf * KTD * D, warp * 16, ts, qpos, qlo, k_begin, k_end,
+                         scale_log2, masked);
     }
     cp_async_wait<0>();
     __syncthreads();
