@@ -353,7 +353,10 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
                    const int* __restrict__ positions, int Hq, int Hkv, int BS, int window, float scale_log2,
                    int NP, int* __restrict__ counters) {
     sb::pdl_launch_dependents();     // the next kernel may begin its prologue
-    sb::pdl_wait();                  // everything before this kernel is complete and visible
+    // What is read before pdl_wait() below was complete before the preceding kernel began:
+    // the block table, rows and positions (copied from the host at the start of the step)
+    // and keys and values below the newest position (written by earlier steps).  The query
+    // and the newest key and value come from the preceding kernel and are read after it.
     constexpr int KTD = 16 * NW;                            // keys per tile
     constexpr int NTHR = 32 * NW;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -382,6 +385,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
 
     const bool empty = k_begin >= k_end;                    // an empty partition (only when NP > 1)
     if (empty) {
+        sb::pdl_wait();
         if (threadIdx.x < G) {
             float* ml = part_ml + (((size_t)n * Hq + h0 + threadIdx.x) * NP + part) * 2;
             ml[0] = -INFINITY;
@@ -394,19 +398,33 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
     const int n_tiles = tile_end - tile_begin;
     for (int i = threadIdx.x; i < pg_end - pg_begin; i += NTHR) stab[i] = table[pg_begin + i];
     __syncthreads();
+    // Tiles that end below the newest key are fetched now, the others after the wait.
+    int s_first_late = 0;
+#pragma unroll
+    for (int s = 0; s < S - 1; ++s) {
+        if (s == s_first_late && s < n_tiles && (tile_begin + s + 1) * KTD <= pos) {
+            load_kv_tile<D, KTD, NTHR>(kbuf + s * KTD * D, vbuf + s * KTD * D, k_pool, v_pool, stab, pg_begin,
+                                       bs_log2, Hkv, kh, (tile_begin + s) * KTD, k_begin, k_end);
+            cp_async_commit();
+            s_first_late = s + 1;
+        }
+    }
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     constexpr int CH = D / 8;
     for (int idx = threadIdx.x; idx < 16 * CH; idx += NTHR) {
         const int row = idx / CH, c = idx - row * CH;
-        const bool valid = row < G;
-        const bf16* src = q + ((size_t)n * Hq + h0 + (valid ? row : 0)) * D + c * 8;
-        cp_async16(smem_u32(qs + tile_off<D>(row, c)), src, valid ? 16 : 0);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)n * Hq + h0 + row) * D + c * 8);
+        *reinterpret_cast<uint4*>(qs + tile_off<D>(row, c)) = v;
     }
 #pragma unroll
     for (int s = 0; s < S - 1; ++s) {
-        if (s < n_tiles)
-            load_kv_tile<D, KTD, NTHR>(kbuf + s * KTD * D, vbuf + s * KTD * D, k_pool, v_pool, stab, pg_begin,
-                                       bs_log2, Hkv, kh, (tile_begin + s) * KTD, k_begin, k_end);
-        cp_async_commit();
+        if (s >= s_first_late) {
+            if (s < n_tiles)
+                load_kv_tile<D, KTD, NTHR>(kbuf + s * KTD * D, vbuf + s * KTD * D, k_pool, v_pool, stab, pg_begin,
+                                           bs_log2, Hkv, kh, (tile_begin + s) * KTD, k_begin, k_end);
+            cp_async_commit();
+        }
     }
 
     const int qpos[2] = {pos, pos};
@@ -631,6 +649,9 @@ extern "C" int sb_attention_decode_mma_blocks_per_sm(int D, int variant) {
 // `counters`: null, or int32 [N * Hkv] that is zero before the first call (and is left zero):
 // then the partition of a (token, KV head) that finishes last merges the partitions itself
 // and no reduce kernel is launched.
+// The block table, rows, positions, and keys and values below each token's position must be
+// complete before the kernel that precedes this one on the stream started; the query and
+// the newest key and value may come from that kernel.
 extern "C" int sb_attention_decode_mma(void* out, float* part_o, float* part_ml, const void* q,
                                        const void* k_pool, const void* v_pool, const int* block_table,
                                        int table_width, const int* token_rows, const int* positions, int N,

@@ -282,7 +282,9 @@ template <typename T, int VPL> struct alignas(sizeof(T) * VPL) Pack { T v[VPL]; 
 
 // The same for head_dim = 32 * VPL with all dims rotating (R == D) or none (R == 0):
 // lane l owns elements l*VPL .. l*VPL+VPL-1, loads and stores them as one vector, and
-// finds its rotation partner (dim +- D/2) in lane l ^ 16.
+// finds its rotation partner (dim +- D/2) in lane l ^ 16.  A block serves `heads_per_block`
+// heads of one token; its first D/2 threads compute the token's cosines and sines once
+// into shared memory, so the trigonometry is not repeated for every head.
 template <typename T, int VPL>
 __global__ void qk_norm_rope_kvwrite_fast_kernel(
     const T* __restrict__ qkv, const float* __restrict__ parts, int S, size_t part_stride,
@@ -290,70 +292,81 @@ __global__ void qk_norm_rope_kvwrite_fast_kernel(
     const float* __restrict__ q_gain, const float* __restrict__ k_gain,
     const float* __restrict__ inv_freq, int R, const int* __restrict__ positions,
     const int* __restrict__ token_rows, const int* __restrict__ block_table, int table_width,
-    int BS, float eps, int Hq, int Hkv, int write_kv) {
+    int BS, float eps, int Hq, int Hkv, int write_kv, int heads_per_block) {
     sb::pdl_launch_dependents();     // the next kernel may begin its prologue
-    sb::pdl_wait();                  // everything before this kernel is complete and visible
     constexpr int D = 32 * VPL;
+    __shared__ float cs[D / 2], sn[D / 2];
     const int n = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int head = blockIdx.y * 4 + warp;
     const int n_heads = Hq + 2 * Hkv;
-    if (head >= n_heads) return;
-    const bool is_q = head < Hq;
-    const bool is_k = !is_q && head < Hq + Hkv;
-    const bool is_v = !is_q && !is_k;
-    if (!is_q && !write_kv) return;
-
-    const size_t base = ((size_t)n * n_heads + head) * D + lane * VPL;
-    float y[VPL];
-    if (parts != nullptr) {
-#pragma unroll
-        for (int i = 0; i < VPL; ++i) y[i] = 0.f;
-        for (int s = 0; s < S; ++s) {
-            const Pack<float, VPL> p = *reinterpret_cast<const Pack<float, VPL>*>(parts + s * part_stride + base);
-#pragma unroll
-            for (int i = 0; i < VPL; ++i) y[i] += p.v[i];
-        }
-    } else {
-        const Pack<T, VPL> p = *reinterpret_cast<const Pack<T, VPL>*>(qkv + base);
-#pragma unroll
-        for (int i = 0; i < VPL; ++i) y[i] = to_float(p.v[i]);
-    }
     const int pos = positions[n];
-    const float* gain = is_q ? q_gain : (is_k ? k_gain : nullptr);
-    if (gain != nullptr) {
-        float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < VPL; ++i) ss += y[i] * y[i];
-        ss = warp_sum(ss);
-        const float rinv = 1.0f / sqrtf(ss / (float)D + eps);
-#pragma unroll
-        for (int i = 0; i < VPL; ++i) y[i] = y[i] * rinv * gain[lane * VPL + i];
-    }
-    Pack<T, VPL> o;
-    if (!is_v && R == D) {
-#pragma unroll
-        for (int i = 0; i < VPL; ++i) {
-            const float partner = __shfl_xor_sync(0xffffffffu, y[i], 16);
-            const float ang = (float)pos * inv_freq[(lane & 15) * VPL + i];
-            const float c = cosf(ang), s = sinf(ang);
-            o.v[i] = from_float<T>(lane < 16 ? y[i] * c - partner * s : y[i] * c + partner * s);
+    if (R == D) {
+        for (int j = threadIdx.x; j < D / 2; j += blockDim.x) {
+            const float ang = (float)pos * inv_freq[j];
+            cs[j] = cosf(ang);
+            sn[j] = sinf(ang);
         }
-    } else {
+    }
+    // positions and inv_freq are older than the preceding kernel (a host copy, a constant
+    // table), so the trigonometry above overlaps that kernel's tail.
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
+    __syncthreads();
+    const int head_end = min(n_heads, (int)(blockIdx.y + 1) * heads_per_block);
+    for (int head = blockIdx.y * heads_per_block + warp; head < head_end; head += blockDim.x >> 5) {
+        const bool is_q = head < Hq;
+        const bool is_k = !is_q && head < Hq + Hkv;
+        const bool is_v = !is_q && !is_k;
+        if (!is_q && !write_kv) break;
+
+        const size_t base = ((size_t)n * n_heads + head) * D + lane * VPL;
+        float y[VPL];
+        if (parts != nullptr) {
 #pragma unroll
-        for (int i = 0; i < VPL; ++i) o.v[i] = from_float<T>(y[i]);
+            for (int i = 0; i < VPL; ++i) y[i] = 0.f;
+            for (int s = 0; s < S; ++s) {
+                const Pack<float, VPL> p = *reinterpret_cast<const Pack<float, VPL>*>(parts + s * part_stride + base);
+#pragma unroll
+                for (int i = 0; i < VPL; ++i) y[i] += p.v[i];
+            }
+        } else {
+            const Pack<T, VPL> p = *reinterpret_cast<const Pack<T, VPL>*>(qkv + base);
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) y[i] = to_float(p.v[i]);
+        }
+        const float* gain = is_q ? q_gain : (is_k ? k_gain : nullptr);
+        if (gain != nullptr) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) ss += y[i] * y[i];
+            ss = warp_sum(ss);
+            const float rinv = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) y[i] = y[i] * rinv * gain[lane * VPL + i];
+        }
+        Pack<T, VPL> o;
+        if (!is_v && R == D) {
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) {
+                const float partner = __shfl_xor_sync(0xffffffffu, y[i], 16);
+                const float c = cs[(lane & 15) * VPL + i], s = sn[(lane & 15) * VPL + i];
+                o.v[i] = from_float<T>(lane < 16 ? y[i] * c - partner * s : y[i] * c + partner * s);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) o.v[i] = from_float<T>(y[i]);
+        }
+        T* dst;
+        if (is_q) {
+            dst = q_out + ((size_t)n * Hq + head) * D;
+        } else {
+            const int kh = is_k ? head - Hq : head - Hq - Hkv;
+            const int row = token_rows[n];
+            const int page = block_table[(size_t)row * table_width + pos / BS];
+            T* pool = is_k ? k_pool : v_pool;
+            dst = pool + (((size_t)page * Hkv + kh) * BS + (pos % BS)) * D;
+        }
+        *reinterpret_cast<Pack<T, VPL>*>(dst + lane * VPL) = o;
     }
-    T* dst;
-    if (is_q) {
-        dst = q_out + ((size_t)n * Hq + head) * D;
-    } else {
-        const int kh = is_k ? head - Hq : head - Hq - Hkv;
-        const int row = token_rows[n];
-        const int page = block_table[(size_t)row * table_width + pos / BS];
-        T* pool = is_k ? k_pool : v_pool;
-        dst = pool + (((size_t)page * Hkv + kh) * BS + (pos % BS)) * D;
-    }
-    *reinterpret_cast<Pack<T, VPL>*>(dst + lane * VPL) = o;
 }
 
 template <typename T>
@@ -362,13 +375,23 @@ static void qk_launch(const void* qkv, const float* parts, int S, size_t part_st
                       int rotary_dim, const int* positions, const int* token_rows, const int* block_table,
                       int table_width, int page_size, float eps, int Hq, int Hkv, int D, int N, int write_kv,
                       cudaStream_t stream) {
-    dim3 grid(N, (Hq + 2 * Hkv + 3) / 4);
     const bool fast = (rotary_dim == D || rotary_dim == 0) && (D == 64 || D == 128 || D == 256);
+    const int n_heads = Hq + 2 * Hkv;
+    // Heads per block: 4 (a head per warp) while that still fills the GPU, more for long batches.
+    int hpb = 4;
+    if (fast) {
+        const long long blocks_wanted = 148LL * 8;
+        hpb = (int)(((long long)N * n_heads + blocks_wanted - 1) / blocks_wanted);
+        hpb = ((hpb + 3) / 4) * 4;
+        if (hpb < 4) hpb = 4;
+        if (hpb > n_heads) hpb = ((n_heads + 3) / 4) * 4;
+    }
+    dim3 grid(N, (n_heads + hpb - 1) / hpb);
 #define SB_QK_ARGS (const T*)qkv, parts, S, part_stride, (T*)q_out, (T*)k_pool, (T*)v_pool, q_gain, k_gain, \
                    inv_freq, rotary_dim, positions, token_rows, block_table, table_width, page_size, eps, Hq, Hkv
-    if (fast && D == 64) sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, 2>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv);
-    else if (fast && D == 128) sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, 4>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv);
-    else if (fast) sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, 8>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv);
+    if (fast && D == 64) sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, 2>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb);
+    else if (fast && D == 128) sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, 4>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb);
+    else if (fast) sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, 8>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb);
     else sb::launch(qk_norm_rope_kvwrite_kernel<T>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, D, write_kv);
 #undef SB_QK_ARGS
 }

@@ -9,11 +9,19 @@ filled by one host-to-device copy before the step; no part reads anything back.
 
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Tuple
 
 import torch
 
 from ..kernels import ops
+
+
+def _l2_prefetch_budget() -> int:
+    """Bytes of the next product's weights that a weight-streaming product asks for in L2 once
+    its own loads are issued (`SOCRATES_L2_PREFETCH_MB`, 0 turns it off).  Measured on the 4B
+    shape: 8 MB shortens a decode step at batch 8 by 1.8 %, 24 MB and more lengthen it."""
+    return int(float(os.environ.get("SOCRATES_L2_PREFETCH_MB", "8")) * (1 << 20))
 
 
 class Buffers:
@@ -104,6 +112,8 @@ class StepContext:
         self.host_batch = host_batch        # the host-side entries; None while a graph is recorded
         self.num_sms = num_sms
         self.status = status                # int32 device word the tensor-core kernels report to
+        self.weight_successor: Dict[int, torch.Tensor] = {}   # set by the model: address -> next weights
+        self.l2_prefetch_bytes = _l2_prefetch_budget()
 
     # ------------------------------------------------------------------ kernel choice
     def uses_tensor_cores(self, x_dtype: torch.dtype, w: torch.Tensor) -> bool:
@@ -138,11 +148,17 @@ class StepContext:
         S = out.shape[0] if out.dim() == 3 else 1
         if self.uses_tensor_cores(x.dtype, w):
             ops.gemm_tcgen05(out if out.dim() == 3 and S > 1 else out.view(out.shape[-2], out.shape[-1]),
-                             x, w, self.status, S, epilogue=epilogue)
+                             x, w, self.status, S, epilogue=epilogue, prefetch=self._next_weights(w))
         else:
             if epilogue:
                 raise ValueError("the fused epilogue exists only in the tensor-core kernel")
             ops.gemm_simt(out, x, w, splits=S)
+
+    def _next_weights(self, w: torch.Tensor):
+        nxt = self.weight_successor.get(w.data_ptr())
+        if nxt is None or self.l2_prefetch_bytes <= 0 or not nxt.is_contiguous():
+            return None
+        return (nxt, self.l2_prefetch_bytes)
 
     def attention_partitions(self, num_kv_heads: int, blocks_per_sm: int, keys_per_part: int) -> int:
         """Into how many key partitions each query's keys are cut.

@@ -48,6 +48,16 @@ class Model:
         self.dtype = dtype
         for part in (self.embedding, *self.layers, self.final_norm, self.head):
             part.bind(tensors, dtype)
+        # The weight matrices in the order in which a step streams them (parts that say so
+        # through streamed_weights()), as a map from each one's address to its successor: a
+        # kernel that streams one can ask for the head of the next in L2.
+        order: List[torch.Tensor] = []
+        for e in self.plan.order:
+            order.extend(getattr(self.layers[e.layer], "streamed_weights", list)())
+        order.extend(getattr(self.head, "streamed_weights", list)())
+        self.weight_successor: Dict[int, torch.Tensor] = {}
+        for w, nxt in zip(order, order[1:]):
+            self.weight_successor.setdefault(w.data_ptr(), nxt)
 
     # ------------------------------------------------------------------ cache
     def cache_needs(self) -> List[Optional[CacheNeeds]]:
@@ -63,6 +73,7 @@ class Model:
 
     # ------------------------------------------------------------------ one step
     def forward(self, ctx: StepContext, cache) -> torch.Tensor:
+        ctx.weight_successor = self.weight_successor
         stream = ResidualStream(self.embedding.forward(ctx))
         for i, e in enumerate(self.plan.order):
             src = e.reads_cache_of

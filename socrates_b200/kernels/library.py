@@ -35,7 +35,7 @@ _SIGNATURES = {
     "sb_sample_slices": [I],
     "sb_gemm_simt": [P, P, P, I, I, I, I, I, I, I, P],
     "sb_attention_simt": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P],
-    "sb_gemm_tcgen05": [P, P, P, I, I, I, I, P, P, I, I, P],
+    "sb_gemm_tcgen05": [P, P, P, I, I, I, I, P, P, I, I, P, LL, P],
     "sb_gemm_tcgen05_splits": [I, I],
     "sb_attention_mma_supports": [I, I, I, I, I],
     "sb_attention_prefill_mma": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],

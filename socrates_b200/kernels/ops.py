@@ -10,7 +10,7 @@ model/kernels/csrc/ops.cpp:29-72.)
 from __future__ import annotations
 
 import ctypes
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -231,12 +231,16 @@ def gemm_tcgen05_splits(K: int, splits: int) -> int:
 
 
 def gemm_tcgen05(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, status: torch.Tensor,
-                 splits: int = 1, variant: int = 0, epilogue: int = 0) -> int:
+                 splits: int = 1, variant: int = 0, epilogue: int = 0,
+                 prefetch: Optional[Tuple[torch.Tensor, int]] = None) -> int:
     """out = a @ w.T on the tcgen05 tensor cores; a [M, K] and w [N, K] bfloat16, K % 8 == 0.
 
     out is bfloat16 or float32 [M, N], or float32 [S, M, N] partial sums where S =
     gemm_tcgen05_splits(K, splits).  `status` is an int32 device tensor that receives a
     non-zero code if a bounded wait inside the kernel gave up.  Returns S.
+    `prefetch`: (tensor, bytes), the leading bytes of the weights that the next product
+    streams; the weight-streaming kernel (M <= 64) asks for them in L2 once its own loads
+    are issued.
     """
     M, K = a.shape
     N = w.shape[0]
@@ -252,8 +256,16 @@ def gemm_tcgen05(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, status: to
         _want(out, "out", torch.float32, (S, M, N))
     lib = library()
     s_io = ctypes.c_int(S)
+    pf_ptr, pf_bytes = None, 0
+    if prefetch is not None and M <= 64:
+        tensor, nbytes = prefetch
+        if not tensor.is_cuda or not tensor.is_contiguous():
+            raise KernelError("a prefetch range must be a contiguous CUDA tensor")
+        pf_ptr = tensor.data_ptr()
+        pf_bytes = max(0, min(int(nbytes), tensor.numel() * tensor.element_size()))
     check(lib, lib.sb_gemm_tcgen05(_ptr(out), _ptr(a), _ptr(w), M, N, K, _code(out.dtype),
-                                   ctypes.byref(s_io), _ptr(status), int(variant), int(epilogue), _stream()),
+                                   ctypes.byref(s_io), _ptr(status), int(variant), int(epilogue),
+                                   pf_ptr, pf_bytes, _stream()),
           "gemm_tcgen05")
     if s_io.value != S:
         raise KernelError(f"gemm_tcgen05 wrote {s_io.value} parts where {S} were expected")
@@ -304,7 +316,11 @@ def attention_decode_mma(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
     of each token cut into `num_partitions` parts; arguments as `attention_simt`.
     `variant` picks the kernel's (warps, stages); 0 is the default.  With `counters` (int32,
     at least N * Hkv entries, zero before the first call and left zero) the partition that
-    finishes last merges the partitions itself and no reduce kernel is launched."""
+    finishes last merges the partitions itself and no reduce kernel is launched.
+
+    The kernel reads the block table, rows, positions and the keys and values below each
+    position before it waits for the kernel that precedes it on the stream: those must be
+    older than that kernel (a host copy, an earlier step)."""
     N = q.shape[0]
     _, Hkv, BS, D = k_pool.shape
     Hq = num_heads

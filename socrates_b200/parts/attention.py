@@ -70,6 +70,10 @@ class GQAAttention(Part):
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds(paged=PagedKVSpec(self.Hkv, self.D, self.window))
 
+    def streamed_weights(self):
+        """The weight matrices in the order in which forward() reads them."""
+        return [self.qkv.weight, self.o.weight]
+
     def forward(self, ctx, x: torch.Tensor, cache) -> Branch:
         N = x.shape[0]
         qkv = self.qkv(ctx, x, "qkv", out="model_or_partial")

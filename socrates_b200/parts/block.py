@@ -44,6 +44,11 @@ class PreNormBlock:
         fn = getattr(self.mixer, "cache_needs", None)
         return fn() if fn is not None else None
 
+    def streamed_weights(self):
+        """Weight matrices in the order in which forward() streams them (optional for a part)."""
+        return [*getattr(self.mixer, "streamed_weights", list)(),
+                *getattr(self.feed_forward, "streamed_weights", list)()]
+
     def forward(self, ctx, stream: ResidualStream, cache) -> None:
         h = self.norms[0].apply(ctx, stream)
         stream.pending = self.mixer.forward(ctx, h, cache)

@@ -52,6 +52,9 @@ class LMHead(Part):
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype) -> None:
         self.linear = Linear(tensors[self.tied_to or self.name + "weight"])
 
+    def streamed_weights(self):
+        return [self.linear.weight]
+
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         return self.linear(ctx, x, "logits", out="float32")
 

@@ -39,6 +39,10 @@ class SwiGLU(Part):
         self.gate_up = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.inter, self.hidden))
         self.down = Linear(tensors[n + "down_proj.weight"])
 
+    def streamed_weights(self):
+        """The weight matrices in the order in which forward() reads them."""
+        return [self.gate_up.weight, self.down.weight]
+
     def forward(self, ctx, x: torch.Tensor) -> Branch:
         N = x.shape[0]
         if ctx.can_fuse_silu_mul(N, self.gate_up.weight, x.dtype):

@@ -98,6 +98,57 @@ def test_gemm_tcgen05_persistent_many_tiles(ops, M, N, K):
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("width", [128, 160, 256])
+def test_gemm_tcgen05_persistent_every_tile_width(ops, width):
+    """Each tile width of the persistent kernel, forced, on a ragged shape with several
+    tiles per block and a last column tile that is cut."""
+    M, N, K = 700, 5 * width + 40, 328
+    a, w, want = operands(M, N, K, seed=width)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N), float("nan"), dtype=dtype, device=DEV)
+        ops.gemm_tcgen05(out, a, w, status, variant=width)
+        close(out, want, K, dtype == torch.bfloat16)
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("width", [128, 160, 192, 256])
+@pytest.mark.parametrize("M,K", [(700, 328), (100, 64), (257, 72), (1024, 2048)])
+def test_gemm_tcgen05_pair_kernel(ops, width, M, K):
+    """The kernel in which two SMs share a tile of 256 rows (cta_group::2), forced, at every
+    tile width: row counts that leave the second block of a pair partly or wholly without rows,
+    a last column tile that is cut, several tiles per pair."""
+    N = 5 * width + 40
+    a, w, want = operands(M, N, K, seed=1000 + width)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N), float("nan"), dtype=dtype, device=DEV)
+        ops.gemm_tcgen05(out, a, w, status, variant=1000 + width)
+        close(out, want, K, dtype == torch.bfloat16)
+    assert int(status.item()) == 0
+
+
+def test_gemm_tcgen05_pair_kernel_is_the_choice_for_many_rows(ops):
+    """8,192 rows of a narrow projection: the default path (the pair kernel there) and the
+    fused SiLU*mul epilogue on it."""
+    M, N, K = 8192, 2560, 512
+    a, w, want = operands(M, N, K, seed=77)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_tcgen05(out, a, w, status)
+    close(out, want, K, False)
+    forced = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_tcgen05(forced, a, w, status, variant=1256)
+    assert torch.equal(out, forced)
+    gate, up = want[:, 0::2], want[:, 1::2]
+    act = torch.full((M, N // 2), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tcgen05(act, a, w, status, epilogue=1)
+    ref = up * gate * torch.sigmoid(gate)
+    err = float((act.double() - ref).abs().max())
+    assert err <= 2 ** -7 * float(ref.abs().max()) + 1e-2, err
+    assert int(status.item()) == 0
+
+
 @pytest.mark.parametrize("M,F,K", [(200, 320, 96), (2048, 9728, 256), (65, 64, 64), (300, 203, 72),
                                    (8, 9728, 2560), (1, 80, 64), (64, 203, 72), (17, 64, 96)])
 def test_gemm_tcgen05_fused_silu_mul(ops, M, F, K):
