@@ -12,10 +12,11 @@
 //   O += P V           tcgen05.mma with A = P from TMEM (hi, then lo on top) and B = V from
 //                      shared memory, MN-major (keys are the K dimension); O stays in TMEM.
 // The weights of tile i are written over the scores of tile i (same TMEM columns), there
-// are two such S/P buffers, a fifth warp does nothing but issue products and a sixth nothing
-// but issue the TMA copies (one box per lane): QK(i+1) goes out before the softmax warps have
-// finished tile i and PV(i) as soon as they have, so the tensor core works on tile i+1's
-// scores and tile i-1's product during tile i's softmax.
+// are two such S/P buffers.  Three more warps only issue work: one the score products, one the
+// P.V products (a thread issues a product about every 80 ns whatever its size, so the two
+// chains have a thread each), one the TMA copies (one box per lane).  QK(i+1) goes out before
+// the softmax warps have finished tile i and PV(i) as soon as they have, so the tensor core
+// works on tile i+1's scores and tile i-1's product during tile i's softmax.
 // O is rescaled lazily: the exponent's reference maximum of a row only moves when the row
 // maximum grows by more than 2^8, and then the row of O in TMEM is multiplied once.
 // Tiles whose keys every row of the block may see skip the position masks.
@@ -178,7 +179,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-constexpr int THREADS = ROWS + 64;   // four softmax warps, the MMA-issuing warp, the copy-issuing warp
+// four softmax warps, the warp that issues the score products, the copy-issuing warp, the warp
+// that issues the P.V products
+constexpr int THREADS = ROWS + 96;
 
 template <int D>
 __global__ void __launch_bounds__(THREADS)
@@ -198,8 +201,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
     __shared__ int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5;
-    const bool issuer = warp == 4;
+    const bool issuer = warp == 4;                          // S = Q K^T
     const bool copier = warp == 5;
+    const bool pv_issuer = warp == 6;                       // O += P V
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_s = base;
     const uint32_t k_s = q_s + q_bytes<D>();               // 2 buffers
@@ -324,14 +328,26 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
             }
         }
     } else if (issuer) {
-        // =============================================================== the MMA-issuing warp
+        // =============================================================== the warp that issues Q K^T
+        // One thread issues a tcgen05.mma about every 80 ns whatever its size (measured), and a
+        // key tile needs 8 products for the scores and 8 for P.V: issued by one thread they, not
+        // the tensor core, set the pace.  So scores and P.V have an issuing thread each; they
+        // write different accumulators and meet only through barriers.
         if (active && (tid & 31) == 0) {
-            bool ok = true;
             constexpr uint32_t idesc_qk = make_idesc(KTILE, false);
-            constexpr uint32_t idesc_pv = make_idesc(D, true);
             const uint64_t dq = desc_kmajor(q_s), dk = desc_kmajor(k_s);
-            const uint64_t dv = desc_mnmajor(v_s, PANEL_KV >> 4);
-            auto issue_qk = [&](int b) {
+            for (int i = 0; i < n_tiles; ++i) {
+                const int b = i & 1;
+                if (!mbar_wait(smem_u32(&k_full[b]), (i >> 1) & 1)) { atomicExch(status, 11); atomicExch(&abort_flag, 1); break; }
+                // S[b] still holds P(i-2), the A operand of PV(i-2).  The tensor core orders
+                // products by their accumulators only, not by an operand read from tensor memory,
+                // so PV(i-2) must have COMPLETED before its weights are overwritten.  v_free[b]
+                // completes once per product on buffer b, and the next one cannot come before the
+                // scores issued here: the wait is never two phases behind.
+                if (i >= 2 && !mbar_wait(smem_u32(&v_free[b]), ((i - 2) >> 1) & 1)) {
+                    atomicExch(status, 13); atomicExch(&abort_flag, 1); break;
+                }
+                if (*((volatile int*)&abort_flag)) break;
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
@@ -341,26 +357,19 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
                     mma_ss(tmem + COL_SP + 64 * b, dq + pq, dk + pk, idesc_qk, kk > 0 ? 1u : 0u);
                 }
                 tc_commit(smem_u32(&s_full[b]));
-            };
-            auto fail = [&](int code) { ok = false; atomicExch(status, code); atomicExch(&abort_flag, 1); };
-
-            if (!mbar_wait(smem_u32(&k_full[0]), 0)) fail(11);
-            if (ok) issue_qk(0);
-            for (int i = 0; i < n_tiles && ok; ++i) {
+            }
+        }
+    } else if (pv_issuer) {
+        // =============================================================== the warp that issues P V
+        if (active && (tid & 31) == 0) {
+            constexpr uint32_t idesc_pv = make_idesc(D, true);
+            const uint64_t dv = desc_mnmajor(v_s, PANEL_KV >> 4);
+            for (int i = 0; i < n_tiles; ++i) {
                 const int b = i & 1;
-                // Scores of the next tile go to S[b^1], which still holds P(i-1), the A operand of
-                // PV(i-1).  The tensor core orders products by their accumulators only, not by an
-                // operand it reads from tensor memory, so PV(i-1) must have COMPLETED before its
-                // weights are overwritten.  (Waiting here, before PV(i) is committed to the same
-                // barrier, also keeps the wait from ever being two phases behind.)
-                if (i + 1 < n_tiles) {
-                    if (!mbar_wait(smem_u32(&k_full[b ^ 1]), ((i + 1) >> 1) & 1)) { fail(11); break; }
-                    if (i > 0 && !mbar_wait(smem_u32(&pv_full), (i - 1) & 1)) { fail(13); break; }
-                    issue_qk(b ^ 1);
-                }
                 // the softmax warps have written P(i) (and zeroed unseen V rows); V(i) has landed
-                if (!mbar_wait(smem_u32(&p_ready[b]), (i >> 1) & 1)) { fail(16); break; }
-                if (!mbar_wait(smem_u32(&v_full[b]), (i >> 1) & 1)) { fail(14); break; }
+                if (!mbar_wait(smem_u32(&p_ready[b]), (i >> 1) & 1)) { atomicExch(status, 16); atomicExch(&abort_flag, 1); break; }
+                if (!mbar_wait(smem_u32(&v_full[b]), (i >> 1) & 1)) { atomicExch(status, 14); atomicExch(&abort_flag, 1); break; }
+                if (*((volatile int*)&abort_flag)) break;
                 tc_fence_after();
                 const uint32_t pbase = tmem + COL_SP + 64 * b;
 #pragma unroll
@@ -371,7 +380,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
                 for (int j = 0; j < KTILE / 16; ++j)
                     mma_ts(tmem + COL_O, pbase + 32 + j * 8, dv + ((b * kv_bytes<D>() + j * 2048) >> 4), idesc_pv, 1u);
                 tc_commit(smem_u32(&pv_full));
-                tc_commit(smem_u32(&v_free[b]));            // V buffer b may be refilled
+                tc_commit(smem_u32(&v_free[b]));            // V buffer b and S/P buffer b may be reused
             }
         }
     } else if (active) {
