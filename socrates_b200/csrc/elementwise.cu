@@ -285,7 +285,7 @@ template <typename T, int VPL> struct alignas(sizeof(T) * VPL) Pack { T v[VPL]; 
 // finds its rotation partner (dim +- D/2) in lane l ^ 16.  A block serves `heads_per_block`
 // heads of one token; its first D/2 threads compute the token's cosines and sines once
 // into shared memory, so the trigonometry is not repeated for every head.
-template <typename T, int VPL>
+template <typename T, int VPL, int U>
 __global__ void qk_norm_rope_kvwrite_fast_kernel(
     const T* __restrict__ qkv, const float* __restrict__ parts, int S, size_t part_stride,
     T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool,
@@ -312,60 +312,80 @@ __global__ void qk_norm_rope_kvwrite_fast_kernel(
     sb::pdl_wait();                  // everything before this kernel is complete and visible
     __syncthreads();
     const int head_end = min(n_heads, (int)(blockIdx.y + 1) * heads_per_block);
-    for (int head = blockIdx.y * heads_per_block + warp; head < head_end; head += blockDim.x >> 5) {
-        const bool is_q = head < Hq;
-        const bool is_k = !is_q && head < Hq + Hkv;
-        const bool is_v = !is_q && !is_k;
-        if (!is_q && !write_kv) break;
-
-        const size_t base = ((size_t)n * n_heads + head) * D + lane * VPL;
-        float y[VPL];
-        if (parts != nullptr) {
+    const int nwarps = blockDim.x >> 5;
+    // U = heads whose loads a warp has in flight at once
+    for (int head0 = blockIdx.y * heads_per_block + warp; head0 < head_end; head0 += U * nwarps) {
+        float y[U][VPL];
 #pragma unroll
-            for (int i = 0; i < VPL; ++i) y[i] = 0.f;
-            for (int s = 0; s < S; ++s) {
-                const Pack<float, VPL> p = *reinterpret_cast<const Pack<float, VPL>*>(parts + s * part_stride + base);
+        for (int u = 0; u < U; ++u) {
+            const int head = head0 + u * nwarps;
+            if (head >= head_end || (head >= Hq && !write_kv)) continue;
+            const size_t base = ((size_t)n * n_heads + head) * D + lane * VPL;
+            if (parts != nullptr) {
 #pragma unroll
-                for (int i = 0; i < VPL; ++i) y[i] += p.v[i];
+                for (int i = 0; i < VPL; ++i) y[u][i] = 0.f;
+                // eight partial sums' loads in flight at a time; added in the order s = 0, 1, ...
+                for (int s0 = 0; s0 < S; s0 += 8) {
+                    Pack<float, VPL> p[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (s0 + j < S)
+                            p[j] = *reinterpret_cast<const Pack<float, VPL>*>(parts + (s0 + j) * part_stride + base);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (s0 + j < S) {
+#pragma unroll
+                            for (int i = 0; i < VPL; ++i) y[u][i] += p[j].v[i];
+                        }
+                }
+            } else {
+                const Pack<T, VPL> p = *reinterpret_cast<const Pack<T, VPL>*>(qkv + base);
+#pragma unroll
+                for (int i = 0; i < VPL; ++i) y[u][i] = to_float(p.v[i]);
             }
-        } else {
-            const Pack<T, VPL> p = *reinterpret_cast<const Pack<T, VPL>*>(qkv + base);
-#pragma unroll
-            for (int i = 0; i < VPL; ++i) y[i] = to_float(p.v[i]);
         }
-        const float* gain = is_q ? q_gain : (is_k ? k_gain : nullptr);
-        if (gain != nullptr) {
-            float ss = 0.f;
 #pragma unroll
-            for (int i = 0; i < VPL; ++i) ss += y[i] * y[i];
-            ss = warp_sum(ss);
-            const float rinv = 1.0f / sqrtf(ss / (float)D + eps);
+        for (int u = 0; u < U; ++u) {
+            const int head = head0 + u * nwarps;
+            if (head >= head_end) continue;
+            const bool is_q = head < Hq;
+            const bool is_k = !is_q && head < Hq + Hkv;
+            const bool is_v = !is_q && !is_k;
+            if (!is_q && !write_kv) continue;
+            const float* gain = is_q ? q_gain : (is_k ? k_gain : nullptr);
+            if (gain != nullptr) {
+                float ss = 0.f;
 #pragma unroll
-            for (int i = 0; i < VPL; ++i) y[i] = y[i] * rinv * gain[lane * VPL + i];
-        }
-        Pack<T, VPL> o;
-        if (!is_v && R == D) {
+                for (int i = 0; i < VPL; ++i) ss += y[u][i] * y[u][i];
+                ss = warp_sum(ss);
+                const float rinv = 1.0f / sqrtf(ss / (float)D + eps);
 #pragma unroll
-            for (int i = 0; i < VPL; ++i) {
-                const float partner = __shfl_xor_sync(0xffffffffu, y[i], 16);
-                const float c = cs[(lane & 15) * VPL + i], s = sn[(lane & 15) * VPL + i];
-                o.v[i] = from_float<T>(lane < 16 ? y[i] * c - partner * s : y[i] * c + partner * s);
+                for (int i = 0; i < VPL; ++i) y[u][i] = y[u][i] * rinv * gain[lane * VPL + i];
             }
-        } else {
+            Pack<T, VPL> o;
+            if (!is_v && R == D) {
 #pragma unroll
-            for (int i = 0; i < VPL; ++i) o.v[i] = from_float<T>(y[i]);
+                for (int i = 0; i < VPL; ++i) {
+                    const float partner = __shfl_xor_sync(0xffffffffu, y[u][i], 16);
+                    const float c = cs[(lane & 15) * VPL + i], s = sn[(lane & 15) * VPL + i];
+                    o.v[i] = from_float<T>(lane < 16 ? y[u][i] * c - partner * s : y[u][i] * c + partner * s);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < VPL; ++i) o.v[i] = from_float<T>(y[u][i]);
+            }
+            T* dst;
+            if (is_q) {
+                dst = q_out + ((size_t)n * Hq + head) * D;
+            } else {
+                const int kh = is_k ? head - Hq : head - Hq - Hkv;
+                const int row = token_rows[n];
+                const int page = block_table[(size_t)row * table_width + pos / BS];
+                T* pool = is_k ? k_pool : v_pool;
+                dst = pool + (((size_t)page * Hkv + kh) * BS + (pos % BS)) * D;
+            }
+            *reinterpret_cast<Pack<T, VPL>*>(dst + lane * VPL) = o;
         }
-        T* dst;
-        if (is_q) {
-            dst = q_out + ((size_t)n * Hq + head) * D;
-        } else {
-            const int kh = is_k ? head - Hq : head - Hq - Hkv;
-            const int row = token_rows[n];
-            const int page = block_table[(size_t)row * table_width + pos / BS];
-            T* pool = is_k ? k_pool : v_pool;
-            dst = pool + (((size_t)page * Hkv + kh) * BS + (pos % BS)) * D;
-        }
-        *reinterpret_cast<Pack<T, VPL>*>(dst + lane * VPL) = o;
     }
 }
 
@@ -389,9 +409,14 @@ static void qk_launch(const void* qkv, const float* parts, int S, size_t part_st
     dim3 grid(N, (n_heads + hpb - 1) / hpb);
 #define SB_QK_ARGS (const T*)qkv, parts, S, part_stride, (T*)q_out, (T*)k_pool, (T*)v_pool, q_gain, k_gain, \
                    inv_freq, rotary_dim, positions, token_rows, block_table, table_width, page_size, eps, Hq, Hkv
-    if (fast && D == 64) sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, 2>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb);
-    else if (fast && D == 128) sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, 4>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb);
-    else if (fast) sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, 8>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb);
+    // Many heads per block (long batches of prompt tokens): four heads' loads in flight per warp.
+#define SB_QK_FAST(VPL_) \
+    if (hpb > 4) sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, VPL_, 4>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb); \
+    else sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, VPL_, 1>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb);
+    if (fast && D == 64) { SB_QK_FAST(2) }
+    else if (fast && D == 128) { SB_QK_FAST(4) }
+    else if (fast) { SB_QK_FAST(8) }
+#undef SB_QK_FAST
     else sb::launch(qk_norm_rope_kvwrite_kernel<T>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, D, write_kv);
 #undef SB_QK_ARGS
 }

@@ -1032,11 +1032,11 @@ int dispatch(const void* A, const void* W, void* C, int M, int N, int K, int spl
         return deep ? launch<64, 8, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream)
                     : launch<64, 4, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
     }
-    // The pair kernel is chosen where its 256 x 256 tiles still make many waves (measured on the
-    // 4B shape: at 8,192 rows the narrow projections gain a fifth, the wide ones 0 to 2 %; at
-    // 2,048 rows nothing is gained, because both kernels are then bound by how the tiles divide
-    // among the SMs), or forced with variant 1000 + width.
-    const bool many_waves = (long)((M + 255) / 256) * ((N + 255) / 256) >= 4L * 74;
+    // The pair kernel is chosen for 4,096 rows and more (measured on the 4B shape: at 8,192 rows
+    // the narrow projections gain a fifth and the wide ones 0 to 2 %; at 2,048 rows the wide ones
+    // lose 3 %, because both kernels are then bound by how the tiles divide among the SMs), or
+    // forced with variant 1000 + width.
+    const bool many_waves = M >= 4096 && (long)((M + 255) / 256) * ((N + 255) / 256) >= 4L * 74;
     if (splits == 1 && N >= 128 && ((variant >= 1128 && variant <= 1256) || (variant == 0 && M > 256 && many_waves))) {
         const int bn = variant == 0 ? 256 : variant - 1000;
         if (!get_map(&ma, A, M, K, BM) || !get_map(&mb, W, N, K, bn / 2)) {
