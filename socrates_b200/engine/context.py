@@ -125,13 +125,22 @@ class StepContext:
     def gemm_splits(self, M: int, w: torch.Tensor, x_dtype: torch.dtype) -> int:
         """Into how many K parts a product whose output is partial sums is cut.
 
-        Only the weight-streaming regime (M <= 64) is cut: enough blocks to keep two
-        resident on every SM, at least two K blocks of 64 each.  A function of the
-        shapes alone, so a recorded graph stays valid.
+        The weight-streaming regime (M <= 64) is cut into enough blocks to keep two resident
+        on every SM, at least two K blocks of 64 each; a product with many rows only where its
+        tiles would leave more than half of the SMs idle.  A function of the shapes alone, so a
+        recorded graph stays valid.
         """
-        if not self.uses_tensor_cores(x_dtype, w) or M > 64:
+        if not self.uses_tensor_cores(x_dtype, w):
             return 1
         N, K = w.shape
+        if M > 64:
+            # Many rows but few tiles (a short prompt portion through a narrow projection): cut K
+            # so that the tiles cover the SMs.  Measured on the 4B shape at 512 rows: o 29 -> 20 us,
+            # down 57 -> 33 us with three parts; from 1,024 rows on a cut no longer pays.
+            tiles = -(-M // 128) * -(-N // 256)
+            if 2 * tiles > self.num_sms:
+                return 1
+            return ops.gemm_tcgen05_splits(K, max(1, min(4, self.num_sms // tiles, (-(-K // 64)) // 8)))
         tiles = -(-N // 128)
         want = max(1, (2 * self.num_sms) // tiles)
         most = max(1, (-(-K // 64)) // 2)
