@@ -1,6 +1,6 @@
 // Paged causal GQA attention of prompt portions on the 5th-generation tensor cores.
 //
-// One block per (query tile, KV head).  A query tile is 128 accumulator rows: 128/G
+// One block per (query tile, KV head).  A query tile is 128 accumulator rows: floor(128/G)
 // consecutive tokens of ONE request times the G query heads of the KV head; row r is
 // TMEM lane r and belongs to thread r for the softmax.  Keys and values come from the
 // pages in tiles of 64 keys, one TMA box per (page, 64-dim panel) into 128-byte swizzled
@@ -29,7 +29,8 @@
 // shared memory before the product, so whatever a previous owner left there cannot reach
 // the result.
 //
-// head_dim 64 or 128, group sizes that divide 128, page sizes 16, 32 or 64.  Every wait on
+// head_dim 64 or 128, any group size up to 128 (128 / G whole tokens a tile, the rows left over idle),
+// page sizes 16, 32 or 64.  Every wait on
 // an mbarrier is bounded; a give-up sets *status, and the block still frees its TMEM.
 #include <cuda.h>
 #include <math.h>
@@ -584,7 +585,7 @@ extern "C" int sb_attention_tcgen05_supports(int Hq, int Hkv, int D, int page_si
     if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return 0;
     if (!(D == 64 || D == 128)) return 0;
     if (!(page_size == 16 || page_size == 32 || page_size == 64)) return 0;
-    return ROWS % (Hq / Hkv) == 0;
+    return Hq / Hkv <= ROWS;       // a group that does not divide 128 leaves the last rows of a tile unused
 }
 
 // Arguments as sb_attention_prefill_mma, plus `num_pages` (pages of the pools, the null

@@ -47,7 +47,8 @@ def status():
 
 
 @pytest.mark.parametrize("Hq,Hkv,D,BS", [(32, 8, 128, 16), (8, 8, 64, 16), (16, 1, 64, 32), (2, 1, 128, 64),
-                                         (8, 2, 128, 16), (4, 2, 64, 64)])
+                                         (8, 2, 128, 16), (4, 2, 64, 64), (40, 8, 128, 16), (9, 3, 64, 32),
+                                         (14, 2, 128, 16)])
 @pytest.mark.parametrize("window", [0, 37, 200])
 def test_prefill_tcgen05_portions_with_earlier_context(ops, ref, Hq, Hkv, D, BS, window):
     lens = [300, 70, 17, 1, 129, 700]
@@ -166,5 +167,7 @@ def test_prefill_tcgen05_far_key_stands_out(ops, ref):
 def test_tcgen05_support_matrix(ops):
     assert ops.attention_tcgen05_supports(32, 8, 128, 16)
     assert not ops.attention_tcgen05_supports(4, 2, 32, 16)            # head size: the mma.sync kernel's
-    assert not ops.attention_tcgen05_supports(9, 3, 64, 16)            # 128 rows do not split into groups of 3
+    assert ops.attention_tcgen05_supports(9, 3, 64, 16)                # groups of 3: 42 tokens a tile, 2 rows idle
+    assert ops.attention_tcgen05_supports(40, 8, 128, 16)              # groups of 5
+    assert not ops.attention_tcgen05_supports(258, 2, 64, 16)          # a group larger than a tile
     assert not ops.attention_tcgen05_supports(32, 8, 128, 128)         # page size
