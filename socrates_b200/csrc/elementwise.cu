@@ -8,13 +8,17 @@ using namespace sb;
 // ----------------------------------------------------------------------------------------
 // Embedding gather: residual[n, :] = float(table[ids[n], :]).
 // The residual stream is float32 in both dtypes of the engine.
+// A negative id -1 - j stands for feedback[j]: a token that an earlier kernel on the stream
+// wrote (the previous step's sample), so that a step can be launched before the host has read
+// the tokens it continues from.
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table,
-                             const int* __restrict__ ids, int d, int V) {
+                             const int* __restrict__ ids, int d, int V, const int* __restrict__ feedback) {
     sb::pdl_launch_dependents();     // the next kernel may begin its prologue
     sb::pdl_wait();                  // everything before this kernel is complete and visible
     const int n = blockIdx.x;
     int id = ids[n];
+    if (id < 0 && feedback != nullptr) id = feedback[-1 - id];
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);   // ids are validated on the host; stay in bounds regardless
     const T* src = table + (size_t)id * d;
     float* dst = out + (size_t)n * d;
@@ -24,12 +28,13 @@ __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ tabl
 // d a multiple of 8 (bfloat16) or 4 (float32): 16-byte loads, one thread per vector.
 template <typename T>
 __global__ void embed_vec_kernel(float* __restrict__ out, const T* __restrict__ table,
-                                 const int* __restrict__ ids, int d, int V) {
+                                 const int* __restrict__ ids, int d, int V, const int* __restrict__ feedback) {
     sb::pdl_launch_dependents();     // the next kernel may begin its prologue
     sb::pdl_wait();                  // everything before this kernel is complete and visible
     constexpr int VEC = Vec16<T>::N;
     const int n = blockIdx.x;
     int id = ids[n];
+    if (id < 0 && feedback != nullptr) id = feedback[-1 - id];
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);
     const T* src = table + (size_t)id * d;
     float* dst = out + (size_t)n * d;
@@ -42,19 +47,20 @@ __global__ void embed_vec_kernel(float* __restrict__ out, const T* __restrict__ 
     }
 }
 
+// feedback: null, or int32 tokens that ids -1 - j refer to (see above).
 extern "C" int sb_embed(float* out, const void* table, const int* ids, int N, int d, int V,
-                        int dtype, cudaStream_t stream) {
+                        int dtype, const int* feedback, cudaStream_t stream) {
     SB_REQUIRE(N >= 0 && d > 0 && V > 0, "embed: bad sizes N=%d d=%d V=%d", N, d, V);
     if (N == 0) return 0;
     const bool aligned = (reinterpret_cast<uintptr_t>(table) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     if (dtype == SB_F32) {
-        if (aligned && d % 4 == 0) sb::launch(embed_vec_kernel<float>, dim3(N), dim3(256), 0, stream, out, (const float*)table, ids, d, V);
-        else sb::launch(embed_kernel<float>, dim3(N), dim3(256), 0, stream, out, (const float*)table, ids, d, V);
+        if (aligned && d % 4 == 0) sb::launch(embed_vec_kernel<float>, dim3(N), dim3(256), 0, stream, out, (const float*)table, ids, d, V, feedback);
+        else sb::launch(embed_kernel<float>, dim3(N), dim3(256), 0, stream, out, (const float*)table, ids, d, V, feedback);
     } else if (dtype == SB_BF16) {
         if (aligned && d % 8 == 0)
-            sb::launch(embed_vec_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, out, (const __nv_bfloat16*)table, ids, d, V);
+            sb::launch(embed_vec_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, out, (const __nv_bfloat16*)table, ids, d, V, feedback);
         else
-            sb::launch(embed_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, out, (const __nv_bfloat16*)table, ids, d, V);
+            sb::launch(embed_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, out, (const __nv_bfloat16*)table, ids, d, V, feedback);
     } else {
         SB_REQUIRE(false, "embed: unknown dtype %d", dtype);
     }

@@ -101,7 +101,7 @@ class StepContext:
     def __init__(self, dtype: torch.dtype, device, buffers: Buffers, num_tokens: int, num_seqs: int,
                  token_ids, positions, token_rows, seq_starts, seq_rows, seq_first_pos, logit_index,
                  all_decode: bool, max_context: int, host_batch=None, num_sms: int = 148,
-                 status: Optional[torch.Tensor] = None):
+                 status: Optional[torch.Tensor] = None, token_feedback: Optional[torch.Tensor] = None):
         self.dtype, self.device, self.buffers = dtype, device, buffers
         self.num_tokens, self.num_seqs = num_tokens, num_seqs
         self.token_ids, self.positions, self.token_rows = token_ids, positions, token_rows
@@ -112,6 +112,7 @@ class StepContext:
         self.host_batch = host_batch        # the host-side entries; None while a graph is recorded
         self.num_sms = num_sms
         self.status = status                # int32 device word the tensor-core kernels report to
+        self.token_feedback = token_feedback   # int32 device tokens that ids -1 - j stand for (see ops.embed)
         self.weight_successor: Dict[int, torch.Tensor] = {}   # set by the model: address -> next weights
         self.l2_prefetch_bytes = _l2_prefetch_budget()
 

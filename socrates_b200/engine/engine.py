@@ -27,7 +27,7 @@ from ..sampling import SamplingParams
 from ..weights import load_weights, random_tensors_on_device
 from .model import Model
 from .runner import ModelRunner, SamplingArgs, StepEntry
-from .scheduler import QueueFull, Request, Scheduler, TooLong
+from .scheduler import PlannedEntry, QueueFull, Request, Scheduler, StepPlan, TooLong
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -60,7 +60,8 @@ class Engine:
     def __init__(self, model, tok=None, device: str = "cuda:0", dtype="bfloat16",
                  compile: bool = True, max_batch: int = 64, max_len: int = 8192,
                  max_new_tokens: int = 1024, block_size: int = 16, num_blocks: Optional[int] = None,
-                 token_budget: int = 2048, max_queue: Optional[int] = None, warmup: bool = False):
+                 token_budget: int = 2048, max_queue: Optional[int] = None, warmup: bool = False,
+                 run_ahead: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("socrates_b200.Engine needs a CUDA device; there is no CPU path")
         require_kernels()                      # fail at start-up, not on the first step
@@ -92,6 +93,12 @@ class Engine:
         self.scheduler = Scheduler(self.cache, max_batch, max_len, self.config.token_budget,
                                    self.config.queue_limit, stop)
         self.steps = 0
+        # run_ahead: while the host waits for a decode step's tokens, the step after it is already
+        # on the GPU (see step()); results are the same with and without
+        self.run_ahead = run_ahead
+        self._ahead = None          # (plan, read handle, sampling args) of a step launched early
+        self._planned = None        # a plan the scheduler made that is not launched yet
+        self.ahead_launched = self.ahead_discarded = 0
         if warmup:
             self.warmup()
 
@@ -132,23 +139,87 @@ class Engine:
         return self.scheduler.submit(req)
 
     # ------------------------------------------------------------------ stepping
-    def step(self) -> bool:
-        """Plan and run one step; False when there was nothing to run."""
-        plan = self.scheduler.plan()
-        if plan is None:
-            return False
+    def _launch(self, plan):
+        """Launch the step of `plan`; returns the handle of its read-back (None: nothing sampled)."""
         entries = [StepEntry(e.row, [e.request.token_at(i) for i in range(e.start, e.start + e.count)],
                              e.start, [e.count - 1] if e.samples else [])
                    for e in plan.entries]
         args = [SamplingArgs(t, s, c) for (t, s, c) in self.scheduler.sampling_args(plan)]
         result = self.runner.step(entries, args)
+        return self.runner.begin_read(len(args)) if result.tokens is not None else None
+
+    def _foresee(self, plan):
+        """The plan of the step after `plan`, if it can be known before `plan`'s tokens are:
+        every live request decodes in `plan`, none can end by length, nobody waits to be
+        admitted, and each row has (or gets) the page for one more token.  None otherwise."""
+        sch = self.scheduler
+        if sch.pending or plan.preempted or len(plan.entries) != sch.n_active:
+            return None
+        entries = []
+        for e in plan.entries:
+            req = e.request
+            if e.count != 1 or not e.samples or len(req.output) + 1 >= req.max_new_tokens:
+                return None
+            if e.start + 2 > self.max_len or not self.cache.reserve(e.row, e.start + 2):
+                return None
+            entries.append((req, e.row, e.start + 1))
+        return entries
+
+    def step(self) -> bool:
+        """Plan and run one step; False when there was nothing to run.
+
+        While the host waits for the tokens of a pure decode step, the step after it is launched
+        already (its tokens stay on the device: the embedding reads what the sampler wrote).
+        When the tokens are in, the scheduler records them and plans; if its plan is the one
+        that was launched, the next call only has to collect it, else the early step is dropped
+        (it wrote nothing that counts: keys past the rows' lengths, tokens nobody reads)."""
+        plan = handle = None
+        if self._ahead is not None:
+            plan, handle, _ = self._ahead
+            self._ahead = None
+            if any(e.request.row != e.row for e in plan.entries):
+                plan = handle = None        # a request left in between (cancelled and swept): drop the early step
+                self.ahead_discarded += 1
+        if plan is None:
+            plan = self._planned if self._planned is not None else self.scheduler.plan()
+            self._planned = None
+            if plan is None:
+                return False
+            handle = self._launch(plan)
+        guess = self._foresee(plan) if (self.run_ahead and handle is not None) else None
+        early = None
+        if guess is not None:
+            early_plan = StepPlan([PlannedEntry(req, row, start, 1, True) for (req, row, start) in guess], [])
+            # sampling counters are those the scheduler will name once this step's tokens are recorded
+            args = [SamplingArgs(req.sampling.temperature, req.sampling.seed, len(req.output) + 1)
+                    for (req, _, _) in guess]
+            entries = [StepEntry(row, [-1 - j], start, [0]) for j, (_, row, start) in enumerate(guess)]
+            self.runner.step(entries, args, ahead=1)
+            early = (early_plan, self.runner.begin_read(len(args)), args)
+            self.ahead_launched += 1
         # the step's one read-back: sampled tokens and the kernels' status word together
-        tokens = self.runner.read_tokens(len(args)) if result.tokens is not None else []
-        if result.tokens is None:
+        tokens = self.runner.finish_read(handle) if handle is not None else []
+        if handle is None:
             self.runner.check_status()
         self.scheduler.complete(plan, tokens)
         self.steps += 1
+        if early is not None:
+            nxt = self.scheduler.plan()
+            if nxt is not None and self._same_step(nxt, early[0], early[2]):
+                self._ahead = (nxt, early[1], early[2])
+            else:
+                self.ahead_discarded += 1
+                self._planned = nxt          # planned (pages reserved): launched by the next call
         return True
+
+    def _same_step(self, plan, early_plan, early_args) -> bool:
+        if plan.preempted or len(plan.entries) != len(early_plan.entries):
+            return False
+        for a, b in zip(plan.entries, early_plan.entries):
+            if a.request is not b.request or a.row != b.row or a.start != b.start or a.count != 1 or not a.samples:
+                return False
+        now = self.scheduler.sampling_args(plan)
+        return all((x.temperature, x.seed, x.counter) == tuple(y) for x, y in zip(early_args, now))
 
     def run(self) -> None:
         """Until every submitted request is finished (model/inference_paged.py:231-237)."""

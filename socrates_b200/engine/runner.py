@@ -86,6 +86,12 @@ class ModelRunner:
         self.status = self._readback[0:1]
         self.sampled = self._readback[1:]
         self._events = [torch.cuda.Event() for _ in self._staging]
+        # read-backs in flight: pinned copies of [status, tokens...], one slot per step that may be
+        # launched before an earlier one's tokens are read
+        self._rb_host = [torch.zeros(max_tokens + 1, dtype=torch.int32).pin_memory() for _ in range(3)]
+        self._rb_np = [b.numpy() for b in self._rb_host]
+        self._rb_events = [torch.cuda.Event() for _ in self._rb_host]
+        self._rb_next = 0
         self.sample_scratch = torch.zeros(ops.sample_scratch_size(max_tokens, self.vocab), dtype=torch.int32,
                                           device=self.device)
         self.use_graphs = use_graphs and model.supports_graph
@@ -106,7 +112,7 @@ class ModelRunner:
             ev.synchronize()
         return buf, i
 
-    def _fill(self, entries: Sequence[StepEntry], sampling) -> Tuple[int, int, int, bool, int]:
+    def _fill(self, entries: Sequence[StepEntry], sampling, ahead: int = 0) -> Tuple[int, int, int, bool, int]:
         L = self.layout
         if not entries:
             raise ValueError("a step needs at least one entry")
@@ -129,13 +135,13 @@ class ModelRunner:
             seen.add(e.row)
             if not 0 <= e.row < self.cache.max_rows:
                 raise ValueError(f"row {e.row} is outside the cache")
-            if e.start != self.cache.lengths[e.row]:
+            if e.start != self.cache.lengths[e.row] + ahead:
                 raise ValueError(f"row {e.row} holds {self.cache.lengths[e.row]} tokens; "
                                  f"the entry starts at {e.start}")
             if e.start + n > self.cache.max_len:
                 raise ValueError(f"row {e.row} would exceed {self.cache.max_len} tokens")
             for t in e.tokens:
-                if not 0 <= t < self.vocab:
+                if not -self.max_tokens <= t < self.vocab:      # -1 - j: the previous step's j-th sample
                     raise ValueError(f"token id {t} is outside the vocabulary of {self.vocab}")
             base = len(ids)
             ids.extend(int(t) for t in e.tokens)
@@ -183,17 +189,32 @@ class ModelRunner:
             seq_first_pos=m[L.seq_first:L.seq_first + R],
             logit_index=m[L.logit:L.logit + M] if M else None,
             all_decode=all_decode, max_context=max_ctx, host_batch=host_batch, num_sms=self.num_sms,
-            status=self.status)
+            status=self.status, token_feedback=self.sampled)
 
-    def read_tokens(self, count: int) -> List[int]:
-        """The `count` tokens the last step sampled, as a host list, and a check of the
-        kernels' status word, in ONE device-to-host copy (which also waits for the step)."""
-        host = self._readback[:count + 1].tolist()
+    def begin_read(self, count: int) -> Tuple[int, int]:
+        """Start the copy of the `count` tokens the last step sampled (and of the kernels'
+        status word) to the host; `finish_read` waits for it.  A later step may be launched in
+        between: the copy is ordered before it on the stream."""
+        slot = self._rb_next
+        self._rb_next = (slot + 1) % len(self._rb_host)
+        self._rb_host[slot][:count + 1].copy_(self._readback[:count + 1], non_blocking=True)
+        self._rb_events[slot].record()
+        return slot, count
+
+    def finish_read(self, handle: Tuple[int, int]) -> List[int]:
+        slot, count = handle
+        self._rb_events[slot].synchronize()
+        host = self._rb_np[slot][:count + 1].tolist()
         if host[0] != 0:
             self.status.zero_()
             raise RuntimeError(f"a tensor-core kernel gave up waiting on its pipeline (code {host[0]}); "
                                f"the step's results are not valid")
         return host[1:]
+
+    def read_tokens(self, count: int) -> List[int]:
+        """The `count` tokens the last step sampled, as a host list, and a check of the
+        kernels' status word, in ONE device-to-host copy (which also waits for the step)."""
+        return self.finish_read(self.begin_read(count))
 
     @torch.no_grad()
     def warmup(self, max_width: int, sample: bool = True) -> int:
@@ -263,11 +284,14 @@ class ModelRunner:
     # ------------------------------------------------------------------ the step
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry],
-             sampling: Optional[Sequence[SamplingArgs]] = None) -> StepResult:
+             sampling: Optional[Sequence[SamplingArgs]] = None, ahead: int = 0) -> StepResult:
         """Run one batch.  The caller has reserved pages for every entry
-        (`cache.reserve(row, start + len(tokens))`) and commits the new lengths after."""
+        (`cache.reserve(row, start + len(tokens))`) and commits the new lengths after.
+        `ahead` = 1: the step is launched before the one before it is committed, so every entry
+        starts one past its row's committed length (and may name its token as -1 - j, the j-th
+        token the step before sampled)."""
         self.cache.flush()
-        N, M, R, all_decode, max_ctx = self._fill(entries, sampling)
+        N, M, R, all_decode, max_ctx = self._fill(entries, sampling, ahead)
         sample = sampling is not None
         self.steps_run += 1
         if self.use_graphs and all_decode and M == N:

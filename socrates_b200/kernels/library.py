@@ -27,7 +27,7 @@ P, I, F, LL = c_void_p, c_int, c_float, c_longlong
 
 _SIGNATURES = {
     "sb_abi_version": [],
-    "sb_embed": [P, P, P, I, I, I, I, P],
+    "sb_embed": [P, P, P, I, I, I, I, P, P],
     "sb_add_rmsnorm": [P, P, I, LL, P, P, P, I, I, F, I, P],
     "sb_qk_norm_rope_kvwrite": [P, P, I, LL, P, P, P, P, P, P, I, P, P, P, I, I, F, I, I, I, I, I, I, P],
     "sb_silu_mul": [P, P, I, I, I, I, P],

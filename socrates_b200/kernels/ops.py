@@ -45,16 +45,21 @@ def _want(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
         raise KernelError(f"{name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
 
 
-def embed(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
-    """out[n, :] = float32(table[ids[n], :]); out float32 [N, d], ids int32 [N]."""
+def embed(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor,
+          feedback: Optional[torch.Tensor] = None) -> None:
+    """out[n, :] = float32(table[ids[n], :]); out float32 [N, d], ids int32 [N].
+    With `feedback` (int32, on the device) an id -1 - j stands for feedback[j]: a token that an
+    earlier kernel on the stream wrote."""
     V, d = table.shape
     N = ids.numel()
     _want(table, "table")
     _want(ids, "ids", torch.int32)
     _want(out, "out", torch.float32, (N, d))
+    if feedback is not None:
+        _want(feedback, "feedback", torch.int32)
     lib = library()
-    check(lib, lib.sb_embed(_ptr(out), _ptr(table), _ptr(ids), N, d, V, _code(table.dtype), _stream()),
-          "embed")
+    check(lib, lib.sb_embed(_ptr(out), _ptr(table), _ptr(ids), N, d, V, _code(table.dtype), _ptr(feedback),
+                            _stream()), "embed")
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor,

@@ -32,7 +32,7 @@ class Embedding(Part):
 
     def forward(self, ctx) -> torch.Tensor:
         out = ctx.buffers.take("residual", ctx.num_tokens, (self.hidden,), torch.float32)
-        ops.embed(out, self.table, ctx.token_ids)
+        ops.embed(out, self.table, ctx.token_ids, ctx.token_feedback)
         return out
 
 

@@ -100,6 +100,41 @@ def test_graphs_and_eager_agree(tmp_path):
     assert a == b
 
 
+@pytest.mark.parametrize("temperature", [0.0, 0.7])
+def test_running_ahead_changes_nothing(tmp_path, temperature):
+    """While the host waits for a decode step's tokens the engine launches the step after it.
+    Requests of different lengths (so that early steps are dropped when one ends), one that
+    arrives while the others decode, one that is cancelled: the same tokens as without, and
+    the bookkeeping holds after every step."""
+    folder = make_folder(tmp_path, "B")
+    ps = prompts_for("B", [20, 7, 33, 12])
+    new = [37, 9, 60, 25]
+    outs = {}
+    for ahead in (False, True):
+        eng = engine_for(folder, "float32", max_batch=4, max_new_tokens=64, run_ahead=ahead)
+        reqs = [eng.submit(p, max_new_tokens=n, temperature=temperature, seed=5 + i)
+                for i, (p, n) in enumerate(zip(ps[:3], new[:3]))]
+        steps = 0
+        while eng.scheduler.has_work():
+            assert eng.step()
+            eng.scheduler.check()
+            steps += 1
+            if steps == 12:                               # a late arrival beside running decodes
+                reqs.append(eng.submit(ps[3], max_new_tokens=new[3], temperature=temperature, seed=8))
+            if steps == 30:
+                reqs[2].cancelled = True                  # leaves at the next plan
+        outs[ahead] = [r.output for r in reqs]
+        assert [len(r.output) for r in reqs[:2]] == new[:2] and len(reqs[3].output) == new[3]
+        assert eng.cache.free_pages() == [g.allocator.num_pages for g in eng.cache.groups]
+        if ahead:
+            assert eng.ahead_launched > 20 and 0 < eng.ahead_discarded < eng.ahead_launched
+        else:
+            assert eng.ahead_launched == 0
+    assert outs[True][:2] == outs[False][:2] and outs[True][3] == outs[False][3]
+    n = min(len(outs[True][2]), len(outs[False][2]))      # the cancelled one: the same tokens while it ran
+    assert n >= 20 and outs[True][2][:n] == outs[False][2][:n]
+
+
 def test_few_pages_preemption_keeps_outputs(tmp_path):
     """A pool too small for all requests at once: some are preempted and recomputed, and
     every request still gets the tokens it gets when it runs alone."""
