@@ -21,12 +21,15 @@
 // sizes that divide 64 (prefill) or are at most 16 (decode); anything else is refused
 // and runs on the SIMT kernel.
 #include <math.h>
+#include <stdlib.h>
 
 #include "attention_reduce.cuh"
 #include "common.cuh"
 
 using namespace sb;
 typedef __nv_bfloat16 bf16;
+
+extern "C" int sb_attention_decode_mma_kernels(int num_partitions, int has_counters);
 
 namespace {
 
@@ -345,7 +348,10 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf
 // ----------------------------------------------------------------------------- decode
 // grid (Hkv, N, NP); every token is one query at position positions[n] of row token_rows[n].
 // NW warps; a key tile holds 16 keys per warp; S stages of tiles are kept in flight.
-template <int D, int NW, int S>
+// CLUSTER: the NP blocks of a (token, KV head) are one thread-block cluster and merge their
+// partial results through distributed shared memory: no scratch in global memory, no reduce
+// kernel.  Every block of the cluster reaches both cluster barriers (an empty partition too).
+template <int D, int NW, int S, bool CLUSTER = false>
 __global__ void __launch_bounds__(32 * NW)
 attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                    const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
@@ -366,6 +372,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
     int* stab = reinterpret_cast<int*>(vbuf + S * KTD * D); // the pages of this partition: up to table_width
     __shared__ float w_m[NW][16], w_l[NW][16];
     __shared__ int s_last;
+    __shared__ float c_ml[16][2];                           // CLUSTER: this partition's (max, sum) per row
 
     const int G = Hq / Hkv;
     const int bs_log2 = 31 - __clz(BS);                     // the page size is a power of two
@@ -384,7 +391,10 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
     const int h0 = kh * G;
 
     const bool empty = k_begin >= k_end;                    // an empty partition (only when NP > 1)
-    if (empty) {
+    if (empty && CLUSTER) {
+        sb::pdl_wait();
+        if (threadIdx.x < 16) { c_ml[threadIdx.x][0] = -INFINITY; c_ml[threadIdx.x][1] = 0.f; }
+    } else if (empty) {
         sb::pdl_wait();
         if (threadIdx.x < G) {
             float* ml = part_ml + (((size_t)n * Hq + h0 + threadIdx.x) * NP + part) * 2;
@@ -489,6 +499,12 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         const int h = h0 + row;
         if (NP == 1) {
             out[((size_t)n * Hq + h) * D + d] = __float2bfloat16_rn(o / L);
+        } else if (CLUSTER) {
+            wo[(size_t)NW * 16 * D + idx] = o;              // behind the warps' rows: [G][D] of this partition
+            if (d == 0) {
+                c_ml[row][0] = M * scale_log2 / LOG2E;      // natural exponents, as in the reduce kernel
+                c_ml[row][1] = L;
+            }
         } else {
             part_o[(((size_t)n * Hq + h) * NP + part) * D + d] = o;
             if (d == 0) {
@@ -499,6 +515,46 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         }
     }
     }   // !empty
+    if constexpr (CLUSTER) {
+        // ---- merge over the cluster: block r writes the outputs idx = r, r + NP, ... of the G x D
+        //      out[h,:] = sum_p e^{m_p - M} o_p / sum_p e^{m_p - M} l_p over partitions with l > 0
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const float* co = reinterpret_cast<const float*>(kbuf) + (size_t)NW * 16 * D;
+        const uint32_t co_addr = static_cast<uint32_t>(__cvta_generic_to_shared(co));
+        const uint32_t ml_addr = static_cast<uint32_t>(__cvta_generic_to_shared(&c_ml[0][0]));
+        for (int idx = part * NTHR + threadIdx.x; idx < G * D; idx += NP * NTHR) {
+            const int row = idx / D;
+            float M = -INFINITY;
+            for (int p = 0; p < NP; ++p) {
+                uint32_t a;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(ml_addr + row * 8), "r"(p));
+                float m, l;
+                asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(m), "=f"(l) : "r"(a) : "memory");
+                if (l > 0.f) M = fmaxf(M, m);
+            }
+            float L = 0.f, o = 0.f;
+            for (int p = 0; p < NP; ++p) {
+                uint32_t a, b;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(ml_addr + row * 8), "r"(p));
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(b) : "r"(co_addr + idx * 4), "r"(p));
+                float m, l;
+                asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(m), "=f"(l) : "r"(a) : "memory");
+                if (l > 0.f) {
+                    float v;
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(b) : "memory");
+                    const float f = expf(m - M);
+                    L += f * l;
+                    o += f * v;
+                }
+            }
+            out[((size_t)n * Hq + h0 + row) * D + (idx - row * D)] = __float2bfloat16_rn(o / L);
+        }
+        // nobody leaves while another block may still read its shared memory
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        return;
+    }
     if (NP == 1 || counters == nullptr) return;
     // ---- the partition that finishes last merges all NP of them (no second launch):
     //      out[h,:] = sum_p e^{m_p - M} o_p / sum_p e^{m_p - M} l_p over partitions with l > 0
@@ -555,21 +611,40 @@ int launch_prefill(void* out, const void* q, const void* k_pool, const void* v_p
     return 0;
 }
 
+// The partitions are merged through the cluster when there are 2 to 4 of them and the caller did
+// not ask for the counter-based merge; SOCRATES_CLUSTER_MERGE=0 keeps the reduce kernel.  Measured
+// in the decode graph of the 4B shape: 4 partitions (batch 8) 2.69 against 2.74 ms a step, 2 (batch
+// 16) 3.25 against 3.31; clusters of 8 (batch 2 to 4) are slower than 9 partitions with the reduce
+// kernel (2.64 against 2.54 ms at batch 4): eight blocks have to find room at the same time.
+inline bool cluster_merge_enabled() {
+    static const bool on = [] { const char* e = getenv("SOCRATES_CLUSTER_MERGE"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
 template <int D, int NW, int S>
 int launch_decode_v(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool, const void* v_pool,
                     const int* block_table, int table_width, const int* token_rows, const int* positions, int N,
                     int Hq, int Hkv, int BS, int window, float scale, int NP, int* counters, cudaStream_t stream) {
-    auto kernel = attn_decode_kernel<D, NW, S>;
     constexpr int smem = decode_smem<D, NW, S>();
+    const bool cluster = sb_attention_decode_mma_kernels(NP, counters != nullptr) == 1 && NP >= 2 && counters == nullptr;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             smem + kMaxTableWidth * 4);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, NW, S, false>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem + kMaxTableWidth * 4);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_decode_kernel<D, NW, S, true>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, smem + kMaxTableWidth * 4);
         if (e != cudaSuccess) { sb_set_error("attention_mma: %s", cudaGetErrorString(e)); return (int)e; }
         configured = true;
     }
     dim3 grid(Hkv, N, NP);
-    sb::launch(kernel, dim3(grid), dim3(32 * NW), smem + table_width * 4, stream, 
+    if (cluster) {
+        sb::launch_cluster(attn_decode_kernel<D, NW, S, true>, dim3(grid), dim3(32 * NW), smem + table_width * 4, stream,
+            dim3(1, 1, NP), (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
+            block_table, table_width, token_rows, positions, Hq, Hkv, BS, window, scale * LOG2E, NP, counters);
+        return 0;
+    }
+    sb::launch(attn_decode_kernel<D, NW, S, false>, dim3(grid), dim3(32 * NW), smem + table_width * 4, stream, 
         (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
         table_width, token_rows, positions, Hq, Hkv, BS, window, scale * LOG2E, NP, counters);
     if (NP > 1 && counters == nullptr) {
@@ -633,6 +708,13 @@ extern "C" int sb_attention_prefill_mma(void* out, const void* q, const void* k_
     }
     if (rc != 0) return rc;
     SB_LAUNCH_CHECK();
+}
+
+// How many kernels sb_attention_decode_mma launches for this many partitions (1, or 2 when a
+// reduce kernel follows): what callers that count launches add.
+extern "C" int sb_attention_decode_mma_kernels(int num_partitions, int has_counters) {
+    if (num_partitions <= 1 || has_counters) return 1;
+    return (num_partitions <= 4 && cluster_merge_enabled()) ? 1 : 2;
 }
 
 // Blocks of the decode kernel that fit one SM at a time (shared memory is the limit):

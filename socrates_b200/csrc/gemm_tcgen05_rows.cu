@@ -483,7 +483,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, in
     }
     const int tiles_m = (M + 255) / 256, tiles_n = (N + BN - 1) / BN;
     const int pairs = min(tiles_m * tiles_n, max_pairs);
-    sb::launch_cluster(kernel, dim3(2 * pairs), dim3(192), smem, stream, 2u, ma, mb, (TC*)C, M, N, K, tiles_m,
+    sb::launch_cluster(kernel, dim3(2 * pairs), dim3(192), smem, stream, dim3(2, 1, 1), ma, mb, (TC*)C, M, N, K, tiles_m,
                        tiles_n, status);
     return 0;
 }

@@ -350,7 +350,7 @@ def attention_decode_mma(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
         _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
         block_table.shape[1], _ptr(token_rows), _ptr(positions), N, Hq, Hkv, D, BS, int(window),
         float(scale), num_partitions, int(variant), _ptr(counters), _stream()), "attention_decode_mma",
-        kernels=2 if num_partitions > 1 and counters is None else 1)
+        kernels=lib.sb_attention_decode_mma_kernels(num_partitions, 0 if counters is None else 1))
 
 
 def attention_decode_mma_blocks_per_sm(head_dim: int, variant: int = 0) -> int:
