@@ -13,7 +13,8 @@
 //   * attn_decode_kernel: one block per (KV head, token, key partition) for steps in
 //     which every request brings one token.  The G query heads are 16 accumulator rows
 //     shared by the four warps; each warp takes a quarter of every key tile and the
-//     warps are merged at the end; partitions are merged by the reduce kernel.
+//     warps are merged at the end; 2 to 4 partitions are merged through the cluster's shared
+//     memory, more by the reduce kernel.
 //
 // Keys outside [lo, hi) are never read from the pool (their shared-memory rows are
 // zero-filled by cp.async and their scores are masked), so whatever a page's previous
@@ -29,7 +30,7 @@
 using namespace sb;
 typedef __nv_bfloat16 bf16;
 
-extern "C" int sb_attention_decode_mma_kernels(int num_partitions, int has_counters);
+extern "C" int sb_attention_decode_mma_kernels(int num_partitions);
 
 namespace {
 
@@ -357,7 +358,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
                    const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                    const int* __restrict__ block_table, int table_width, const int* __restrict__ token_rows,
                    const int* __restrict__ positions, int Hq, int Hkv, int BS, int window, float scale_log2,
-                   int NP, int* __restrict__ counters) {
+                   int NP) {
     sb::pdl_launch_dependents();     // the next kernel may begin its prologue
     // What is read before pdl_wait() below was complete before the preceding kernel began:
     // the block table, rows and positions (copied from the host at the start of the step)
@@ -371,7 +372,6 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
     bf16* vbuf = kbuf + S * KTD * D;                        // S x [KTD][D]
     int* stab = reinterpret_cast<int*>(vbuf + S * KTD * D); // the pages of this partition: up to table_width
     __shared__ float w_m[NW][16], w_l[NW][16];
-    __shared__ int s_last;
     __shared__ float c_ml[16][2];                           // CLUSTER: this partition's (max, sum) per row
 
     const int G = Hq / Hkv;
@@ -401,7 +401,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
             ml[0] = -INFINITY;
             ml[1] = 0.f;
         }
-        if (counters == nullptr) return;                    // the reduce kernel follows
+        return;                                             // the reduce kernel follows
     }
     if (!empty) {
     const int tile_begin = k_begin / KTD, tile_end = (k_end + KTD - 1) / KTD;
@@ -555,36 +555,6 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         return;
     }
-    if (NP == 1 || counters == nullptr) return;
-    // ---- the partition that finishes last merges all NP of them (no second launch):
-    //      out[h,:] = sum_p e^{m_p - M} o_p / sum_p e^{m_p - M} l_p over partitions with l > 0
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const int prev = atomicAdd(&counters[n * Hkv + kh], 1);
-        s_last = prev == NP - 1;
-        if (s_last) counters[n * Hkv + kh] = 0;             // ready for the next launch
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    for (int idx = threadIdx.x; idx < G * D; idx += NTHR) {
-        const int row = idx / D, d = idx - row * D;
-        const size_t slot = ((size_t)n * Hq + h0 + row) * NP;
-        float M = -INFINITY;
-        for (int p = 0; p < NP; ++p)
-            if (__ldcg(part_ml + (slot + p) * 2 + 1) > 0.f) M = fmaxf(M, __ldcg(part_ml + (slot + p) * 2));
-        float L = 0.f, o = 0.f;
-        for (int p = 0; p < NP; ++p) {
-            const float l = __ldcg(part_ml + (slot + p) * 2 + 1);
-            if (l > 0.f) {
-                const float f = expf(__ldcg(part_ml + (slot + p) * 2) - M);
-                L += f * l;
-                o += f * __ldcg(part_o + (slot + p) * D + d);
-            }
-        }
-        out[((size_t)n * Hq + h0 + row) * D + d] = __float2bfloat16_rn(o / L);
-    }
 }
 
 template <int D> constexpr int prefill_smem() { return (64 * D + 4 * KT * D) * 2; }
@@ -611,8 +581,8 @@ int launch_prefill(void* out, const void* q, const void* k_pool, const void* v_p
     return 0;
 }
 
-// The partitions are merged through the cluster when there are 2 to 4 of them and the caller did
-// not ask for the counter-based merge; SOCRATES_CLUSTER_MERGE=0 keeps the reduce kernel.  Measured
+// The partitions are merged through the cluster when there are 2 to 4 of them;
+// SOCRATES_CLUSTER_MERGE=0 keeps the reduce kernel.  Measured
 // in the decode graph of the 4B shape: 4 partitions (batch 8) 2.69 against 2.74 ms a step, 2 (batch
 // 16) 3.25 against 3.31; clusters of 8 (batch 2 to 4) are slower than 9 partitions with the reduce
 // kernel (2.64 against 2.54 ms at batch 4): eight blocks have to find room at the same time.
@@ -624,9 +594,9 @@ inline bool cluster_merge_enabled() {
 template <int D, int NW, int S>
 int launch_decode_v(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool, const void* v_pool,
                     const int* block_table, int table_width, const int* token_rows, const int* positions, int N,
-                    int Hq, int Hkv, int BS, int window, float scale, int NP, int* counters, cudaStream_t stream) {
+                    int Hq, int Hkv, int BS, int window, float scale, int NP, cudaStream_t stream) {
     constexpr int smem = decode_smem<D, NW, S>();
-    const bool cluster = sb_attention_decode_mma_kernels(NP, counters != nullptr) == 1 && NP >= 2 && counters == nullptr;
+    const bool cluster = NP >= 2 && sb_attention_decode_mma_kernels(NP) == 1;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, NW, S, false>,
@@ -641,38 +611,33 @@ int launch_decode_v(void* out, float* part_o, float* part_ml, const void* q, con
     if (cluster) {
         sb::launch_cluster(attn_decode_kernel<D, NW, S, true>, dim3(grid), dim3(32 * NW), smem + table_width * 4, stream,
             dim3(1, 1, NP), (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
-            block_table, table_width, token_rows, positions, Hq, Hkv, BS, window, scale * LOG2E, NP, counters);
+            block_table, table_width, token_rows, positions, Hq, Hkv, BS, window, scale * LOG2E, NP);
         return 0;
     }
     sb::launch(attn_decode_kernel<D, NW, S, false>, dim3(grid), dim3(32 * NW), smem + table_width * 4, stream, 
         (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
-        table_width, token_rows, positions, Hq, Hkv, BS, window, scale * LOG2E, NP, counters);
-    if (NP > 1 && counters == nullptr) {
+        table_width, token_rows, positions, Hq, Hkv, BS, window, scale * LOG2E, NP);
+    if (NP > 1) {
         dim3 rgrid(Hq, N);
         sb::launch(attn_reduce_kernel<bf16>, dim3(rgrid), dim3(128), 0, stream, (bf16*)out, part_o, part_ml, Hq, D, NP);
     }
     return 0;
 }
 
-// Shapes of the decode kernel: (warps, stages).  Variant 0 is the default.
-constexpr int kDecodeVariants = 5;
-constexpr int kVariantWarps[kDecodeVariants] = {4, 4, 2, 2, 4};
-constexpr int kVariantStages[kDecodeVariants] = {3, 2, 4, 6, 4};
+// Shapes of the decode kernel: (warps, stages).  Variant 0 is the default; variant 1 holds one
+// stage less, so that three blocks fit an SM.  (Two warps with rings of 4 or 6 stages and four
+// warps with 4 stages were measured slower at every batch size and are gone.)
+constexpr int kDecodeVariants = 2;
+constexpr int kVariantWarps[kDecodeVariants] = {4, 4};
+constexpr int kVariantStages[kDecodeVariants] = {3, 2};
 
 template <int D>
 int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool, const void* v_pool,
                   const int* block_table, int table_width, const int* token_rows, const int* positions, int N,
-                  int Hq, int Hkv, int BS, int window, float scale, int NP, cudaStream_t stream, int variant = 0,
-                  int* counters = nullptr) {
+                  int Hq, int Hkv, int BS, int window, float scale, int NP, cudaStream_t stream, int variant = 0) {
 #define SB_DEC(NW, S) launch_decode_v<D, NW, S>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, \
-                                                token_rows, positions, N, Hq, Hkv, BS, window, scale, NP, counters, stream)
-    switch (variant) {
-        case 1: return SB_DEC(4, 2);
-        case 2: return SB_DEC(2, 4);
-        case 3: return SB_DEC(2, 6);
-        case 4: return SB_DEC(4, 4);
-        default: return SB_DEC(4, 3);
-    }
+                                                token_rows, positions, N, Hq, Hkv, BS, window, scale, NP, stream)
+    return variant == 1 ? SB_DEC(4, 2) : SB_DEC(4, 3);
 #undef SB_DEC
 }
 
@@ -712,8 +677,8 @@ extern "C" int sb_attention_prefill_mma(void* out, const void* q, const void* k_
 
 // How many kernels sb_attention_decode_mma launches for this many partitions (1, or 2 when a
 // reduce kernel follows): what callers that count launches add.
-extern "C" int sb_attention_decode_mma_kernels(int num_partitions, int has_counters) {
-    if (num_partitions <= 1 || has_counters) return 1;
+extern "C" int sb_attention_decode_mma_kernels(int num_partitions) {
+    if (num_partitions <= 1) return 1;
     return (num_partitions <= 4 && cluster_merge_enabled()) ? 1 : 2;
 }
 
@@ -728,9 +693,6 @@ extern "C" int sb_attention_decode_mma_blocks_per_sm(int D, int variant) {
 
 // Steps in which every request brings one token.  Scratch as for sb_attention_simt.
 // `variant` selects (warps, stages) of the kernel; 0 is the default.
-// `counters`: null, or int32 [N * Hkv] that is zero before the first call (and is left zero):
-// then the partition of a (token, KV head) that finishes last merges the partitions itself
-// and no reduce kernel is launched.
 // The block table, rows, positions, and keys and values below each token's position must be
 // complete before the kernel that precedes this one on the stream started; the query and
 // the newest key and value may come from that kernel.
@@ -738,7 +700,7 @@ extern "C" int sb_attention_decode_mma(void* out, float* part_o, float* part_ml,
                                        const void* k_pool, const void* v_pool, const int* block_table,
                                        int table_width, const int* token_rows, const int* positions, int N,
                                        int Hq, int Hkv, int D, int page_size, int window, float scale,
-                                       int num_partitions, int variant, int* counters, cudaStream_t stream) {
+                                       int num_partitions, int variant, cudaStream_t stream) {
     SB_REQUIRE(sb_attention_mma_supports(Hq, Hkv, D, page_size, 1),
                "attention_mma (decode): Hq=%d Hkv=%d head_dim=%d is not supported", Hq, Hkv, D);
     SB_REQUIRE(N > 0 && N <= 65535 && window >= 0 && table_width > 0, "attention_mma: bad sizes N=%d", N);
@@ -749,10 +711,10 @@ extern "C" int sb_attention_decode_mma(void* out, float* part_o, float* part_ml,
                "attention_mma: split over %d partitions needs scratch buffers", num_partitions);
     int rc;
     switch (D) {
-        case 16: rc = launch_decode<16>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant, counters); break;
-        case 32: rc = launch_decode<32>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant, counters); break;
-        case 64: rc = launch_decode<64>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant, counters); break;
-        default: rc = launch_decode<128>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant, counters); break;
+        case 16: rc = launch_decode<16>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant); break;
+        case 32: rc = launch_decode<32>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant); break;
+        case 64: rc = launch_decode<64>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant); break;
+        default: rc = launch_decode<128>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, token_rows, positions, N, Hq, Hkv, page_size, window, scale, num_partitions, stream, variant); break;
     }
     if (rc != 0) return rc;
     SB_LAUNCH_CHECK();

@@ -350,24 +350,18 @@ int dispatch(const void* A, const void* W, void* C, int M, int N, int K, int spl
             return SB_ERR_ARG;
         }
         dim3 grid((N + BM - 1) / BM, 1, splits);
-        // Weight streaming.  Two ring depths: the shallow one leaves room for two blocks on
-        // an SM (and for the next kernel's blocks to start their prologue beside it), the
-        // deep one fills an SM's shared memory from a single block.  Measured back to back
-        // in a graph the shallow ring is faster for every projection of the 4B shape
-        // (qkv 7.6 vs 10.3 us, gate_up 19.1 vs 33.7 us), so it is the default; variant 2
-        // selects the deep one.
-        const bool deep = variant == 2;
+        // Weight streaming.  The ring leaves room for two blocks on an SM (and for the next kernel's
+        // blocks to start their prologue beside it).  Rings of 3 to 5 stages and one that fills an
+        // SM's shared memory from a single block were measured slower in the decode graph of the
+        // 4B shape (2.78 to 3.05 against 2.75 ms a step).
         if (epi == 1) {
             if (bn == 16) return launch<16, 6, true, TC, 1>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
             if (bn == 32) return launch<32, 5, true, TC, 1>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
             return launch<64, 4, true, TC, 1>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
         }
-        if (bn == 16) return deep ? launch<16, 12, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream)
-                                  : launch<16, 6, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
-        if (bn == 32) return deep ? launch<32, 10, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream)
-                                  : launch<32, 5, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
-        return deep ? launch<64, 8, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream)
-                    : launch<64, 4, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
+        if (bn == 16) return launch<16, 6, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
+        if (bn == 32) return launch<32, 5, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
+        return launch<64, 4, true, TC>(ma, mb, C, M, N, K, grid, kb_per_split, status, stream);
     }
     if (splits == 1 && N >= 128 && variant != 4)      // the persistent kernels (gemm_tcgen05_rows.cu)
         return sb::gemm_tcgen05_many_rows(A, W, C, M, N, K, sizeof(TC) == 2 ? SB_BF16 : SB_F32, status, variant, epi, stream);
@@ -393,9 +387,8 @@ int dispatch(const void* A, const void* W, void* C, int M, int N, int K, int spl
 // C: c_dtype [M,N] when the effective split count is 1, else float32 [splits, M, N].
 // *splits_io: wanted number of K parts in, number actually written out (never more).
 // status: device int the kernel writes a non-zero code to if a bounded wait gave up.
-// variant: 0 or 1 = shallow ring of the weight-streaming kernel (two blocks per SM),
-//          2 = deep ring (one block per SM); 4 = one tile per block also for many rows
-//          (the default there is the persistent kernel); 128, 144, ..., 256 = that tile width
+// variant: 0 = the kernels chosen by shape; 4 = one tile per block also for many rows
+//          (the default there is the persistent kernel); 128, 160, 256 = that tile width
 //          in the persistent kernel instead of the one it would choose; 1128, 1160, 1192,
 //          1256 = the pair kernel (two SMs per tile, cta_group::2) with tiles 256 x (variant - 1000).
 // epilogue: 0 = C[M,N]; 1 = W interleaves gate and up rows and C is [M, N/2] = up * silu(gate)

@@ -61,19 +61,6 @@ class Buffers:
             self._flat[key] = buf
         return buf[:numel]
 
-    def take_zeroed(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
-        """A flat buffer that is zero when it is created; kernels that use it (counters)
-        leave it zero.  Grows like `take_flat`."""
-        key = (name, dtype)
-        buf = self._flat.get(key)
-        if buf is None or buf.numel() < numel:
-            if buf is not None:
-                self._retired.append(buf)
-            size = max(numel, 2 * buf.numel() if buf is not None else numel)
-            buf = torch.zeros(size, dtype=dtype, device=self.device)
-            self._flat[key] = buf
-        return buf[:numel]
-
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size()
                    for t in [*self._by_name.values(), *self._flat.values(), *self._retired])
@@ -213,10 +200,6 @@ class StepContext:
             part_o = self.buffers.take_flat("attn_part_o", N * num_heads * NP * D, torch.float32)
             part_ml = self.buffers.take_flat("attn_part_ml", N * num_heads * NP * 2, torch.float32)
         if use_mma:
-            # The partitions are merged by the reduce kernel.  (The decode kernel can also let
-            # the partition that finishes last do the merge, `counters=`; measured in the decode
-            # graph of the 4B shape that is slower: 2.98 against 2.90 ms a step at batch 8, 2.88
-            # against 2.43 ms at batch 1, since one block merges what 4 * Hkv blocks merge here.)
             ops.attention_decode_mma(out, q, k_pool, v_pool, table, self.token_rows, self.positions, num_heads,
                                      scale, window, NP, part_o, part_ml)
         else:

@@ -39,9 +39,9 @@ _SIGNATURES = {
     "sb_gemm_tcgen05_splits": [I, I],
     "sb_attention_mma_supports": [I, I, I, I, I],
     "sb_attention_prefill_mma": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],
-    "sb_attention_decode_mma": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P],
+    "sb_attention_decode_mma": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P],
     "sb_attention_decode_mma_blocks_per_sm": [I, I],
-    "sb_attention_decode_mma_kernels": [I, I],
+    "sb_attention_decode_mma_kernels": [I],
     "sb_attention_tcgen05_supports": [I, I, I, I],
     "sb_attention_prefill_tcgen05": [P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P],
 }

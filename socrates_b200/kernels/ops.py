@@ -315,13 +315,12 @@ def attention_decode_mma(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
                          block_table: torch.Tensor, token_rows: torch.Tensor, positions: torch.Tensor,
                          num_heads: int, scale: float, window: int = 0, num_partitions: int = 1,
                          part_o: Optional[torch.Tensor] = None,
-                         part_ml: Optional[torch.Tensor] = None, variant: int = 0,
-                         counters: Optional[torch.Tensor] = None) -> None:
+                         part_ml: Optional[torch.Tensor] = None, variant: int = 0) -> None:
     """Paged attention of single decode tokens on the tensor cores (bfloat16), the keys
     of each token cut into `num_partitions` parts; arguments as `attention_simt`.
-    `variant` picks the kernel's (warps, stages); 0 is the default.  With `counters` (int32,
-    at least N * Hkv entries, zero before the first call and left zero) the partition that
-    finishes last merges the partitions itself and no reduce kernel is launched.
+    `variant` picks the kernel's (warps, stages); 0 is the default.  2 to 4 partitions are
+    merged inside the kernel (a thread-block cluster per token and KV head), more by a
+    reduce kernel through the scratch buffers.
 
     The kernel reads the block table, rows, positions and the keys and values below each
     position before it waits for the kernel that precedes it on the stream: those must be
@@ -341,16 +340,12 @@ def attention_decode_mma(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
         _want(part_ml, "part_ml", torch.float32)
         if part_o.numel() < N * Hq * num_partitions * D or part_ml.numel() < N * Hq * num_partitions * 2:
             raise KernelError("attention scratch buffers are too small")
-    if counters is not None:
-        _want(counters, "counters", torch.int32)
-        if counters.numel() < N * Hkv:
-            raise KernelError("attention counters are too small")
     lib = library()
     check(lib, lib.sb_attention_decode_mma(
         _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
         block_table.shape[1], _ptr(token_rows), _ptr(positions), N, Hq, Hkv, D, BS, int(window),
-        float(scale), num_partitions, int(variant), _ptr(counters), _stream()), "attention_decode_mma",
-        kernels=lib.sb_attention_decode_mma_kernels(num_partitions, 0 if counters is None else 1))
+        float(scale), num_partitions, int(variant), _stream()), "attention_decode_mma",
+        kernels=lib.sb_attention_decode_mma_kernels(num_partitions))
 
 
 def attention_decode_mma_blocks_per_sm(head_dim: int, variant: int = 0) -> int:
