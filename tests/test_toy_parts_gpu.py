@@ -192,3 +192,191 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path, dtype, tol):
     finally:
         unregister_part("mixer", "toy_decay")
         unregister_architecture(ToyConfig.architecture)
+
+
+# ------------------------------------------------------------------------------------------
+# A feed-forward with routing and another position encoding, defined here.
+
+E_EXPERTS, E_FF = 3, 40
+
+
+def make_routed():
+    from socrates_b200.parts import Branch, ParamSpec, Part
+    from socrates_b200.parts.linear import Linear
+
+    class RoutedFF(Part):
+        """Top-1 of E experts per token: router logits and their softmax in float32, tokens
+        gathered per expert, each expert up -> SiLU -> down through the engine's own products,
+        outputs scattered back times the router's probability."""
+        supports_graph = False          # how many tokens an expert gets is known on the host only
+
+        def __init__(self, spec, name):
+            super().__init__(spec, name)
+            self.d, self.f, self.E = spec.params["hidden_size"], spec.params["expert_size"], spec.params["experts"]
+
+        def parameters(self):
+            # role "gain": held as float32 on the device whatever the model dtype is
+            p = {self.name + "router.weight": ParamSpec((self.E, self.d), role="gain", init="normal")}
+            for e in range(self.E):
+                p[f"{self.name}experts.{e}.up.weight"] = ParamSpec((self.f, self.d))
+                p[f"{self.name}experts.{e}.down.weight"] = ParamSpec((self.d, self.f))
+            return p
+
+        def bind(self, tensors, dtype):
+            self.router = tensors[self.name + "router.weight"].float()
+            self.up = [Linear(tensors[f"{self.name}experts.{e}.up.weight"]) for e in range(self.E)]
+            self.down = [Linear(tensors[f"{self.name}experts.{e}.down.weight"]) for e in range(self.E)]
+
+        def forward(self, ctx, x):
+            probs = torch.softmax(x.float() @ self.router.T, dim=-1)          # float32
+            top_p, top_e = probs.max(dim=-1)
+            out = torch.zeros(1, x.shape[0], self.d, dtype=torch.float32, device=x.device)
+            for e in range(self.E):
+                rows = (top_e == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                xe = x.index_select(0, rows).contiguous()
+                h = self.up[e](ctx, xe, f"toy_up{e}", out="float32")
+                h = (h * torch.sigmoid(h)).to(x.dtype)
+                y = self.down[e](ctx, h, f"toy_down{e}", out="float32")
+                out[0].index_copy_(0, rows, y * top_p[rows, None])
+            return Branch(out)
+
+    return RoutedFF
+
+
+def make_linear_position():
+    from socrates_b200.parts import Part
+
+    class LinearFrequencies(Part):
+        """Frequencies that fall linearly, not geometrically, over the first `rotary_dim` dims."""
+
+        def __init__(self, spec, name=""):
+            super().__init__(spec, name)
+            self.rotary_dim, self.top = int(spec.params["rotary_dim"]), float(spec.params["top"])
+            self._table = None
+
+        def inv_freq(self):
+            n = self.rotary_dim // 2
+            return self.top * (1.0 - torch.arange(n).float() / n)
+
+        def tables(self, device):
+            if self._table is None:
+                self._table = self.inv_freq().to(device=device, dtype=torch.float32).contiguous()
+            return self._table, self.rotary_dim
+
+    return LinearFrequencies
+
+
+@dataclass(frozen=True)
+class RoutedConfig:
+    architecture = "ToyRoutedForCausalLM"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls()
+
+    def to_dict(self):
+        return {"architectures": [self.architecture], "vocab_size": VOCAB}
+
+    def plan(self):
+        from socrates_b200.config import LayerSpec, ModelPlan, PartSpec, RunEntry
+        norm = {"dim": D_MODEL, "eps": 1e-5}
+        norms = (PartSpec("rmsnorm", norm, "n1."), PartSpec("rmsnorm", norm, "n2."))
+
+        def attn(position):
+            return PartSpec("gqa_attention", {
+                "hidden_size": D_MODEL, "num_heads": HEADS, "num_kv_heads": KV, "head_dim": HD,
+                "scale": HD ** -0.5, "qk_norm_eps": None, "window": None, "position": position}, "attn.")
+        routed = PartSpec("toy_routed", {"hidden_size": D_MODEL, "expert_size": E_FF, "experts": E_EXPERTS}, "moe.")
+        dense = PartSpec("swiglu", {"hidden_size": D_MODEL, "intermediate_size": FF}, "mlp.")
+        layers = (LayerSpec("pre_norm", "layers.0.", norms,
+                            attn(PartSpec("toy_linear_freq", {"rotary_dim": 8, "top": 0.5})), routed),
+                  LayerSpec("pre_norm", "layers.1.", norms,
+                            attn(PartSpec("rotary", {"head_dim": HD, "rotary_dim": 12, "theta": 1e3})), dense))
+        return ModelPlan(self.architecture, D_MODEL, VOCAB,
+                         PartSpec("embedding", {"vocab_size": VOCAB, "hidden_size": D_MODEL}, "embed."),
+                         layers, (RunEntry(0), RunEntry(1)), PartSpec("rmsnorm", norm, "norm."),
+                         PartSpec("lm_head", {"hidden_size": D_MODEL, "vocab_size": VOCAB, "tied_to": "embed.weight"},
+                                  "head."))
+
+
+def plain_routed(w, ids):
+    w = {k: v.double() for k, v in w.items()}
+    T = len(ids)
+    pos = torch.arange(T)
+    x = w["embed.weight"][torch.tensor(ids)]
+
+    def rotate(t, inv_freq, R):
+        ang = pos[:, None].double() * inv_freq[None, :].double()
+        cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        a, b, rest = t[..., :R // 2], t[..., R // 2:R], t[..., R:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin, rest], dim=-1)
+
+    def attention(x, i, inv_freq, R):
+        p = f"layers.{i}.attn."
+        h = plain.rms_norm(x, w[f"layers.{i}.n1.weight"], 1e-5)
+        q = rotate((h @ w[p + "q_proj.weight"].T).view(T, HEADS, HD), inv_freq, R)
+        k = rotate((h @ w[p + "k_proj.weight"].T).view(T, KV, HD), inv_freq, R)
+        v = (h @ w[p + "v_proj.weight"].T).view(T, KV, HD)
+        o = plain.attention_core(q, k, v, HD ** -0.5, plain.attention_mask(pos, pos, None))
+        return x + o.reshape(T, HEADS * HD) @ w[p + "o_proj.weight"].T
+
+    x = attention(x, 0, 0.5 * (1.0 - torch.arange(4).float() / 4), 8)
+    h = plain.rms_norm(x, w["layers.0.n2.weight"], 1e-5)
+    probs = torch.softmax(h @ w["layers.0.moe.router.weight"].T, dim=-1)
+    top_p, top_e = probs.max(dim=-1)
+    y = torch.zeros_like(x)
+    for t in range(T):
+        e = int(top_e[t])
+        u = h[t] @ w[f"layers.0.moe.experts.{e}.up.weight"].T
+        y[t] = top_p[t] * ((u * torch.sigmoid(u)) @ w[f"layers.0.moe.experts.{e}.down.weight"].T)
+    x = x + y
+    x = attention(x, 1, 1.0 / (1e3 ** (torch.arange(0, 12, 2).float() / 12)), 12)
+    x = x + plain.swiglu(plain.rms_norm(x, w["layers.1.n2.weight"], 1e-5), w, "layers.1.mlp.")
+    return plain.rms_norm(x, w["norm.weight"], 1e-5) @ w["embed.weight"].T
+
+
+def test_toy_routed_feed_forward_and_position_encoding(tmp_path):
+    """A routed feed-forward and a position encoding of its own, registered from here: one
+    layer uses both, the next the built-in rotation over 12 of 16 dims (a rotation that is
+    neither all dims nor none) and no QK norm; float32, prompt portions then single tokens."""
+    from safetensors.torch import load_file
+    from socrates_b200.cache import CacheManager
+    from socrates_b200.config import register_architecture, unregister_architecture
+    from socrates_b200.engine.engine import build_model
+    from socrates_b200.engine.runner import ModelRunner, StepEntry
+    from socrates_b200.parts import register_part, unregister_part
+    from socrates_b200.weights import write_model_folder
+
+    register_part("feed_forward", "toy_routed", make_routed())
+    register_part("position", "toy_linear_freq", make_linear_position())
+    register_architecture(RoutedConfig.architecture, RoutedConfig)
+    try:
+        folder = write_model_folder(RoutedConfig(), seed=9, out_dir=tmp_path / "routed")
+        w = load_file(str(folder / "model.safetensors"))
+        config, model = build_model(folder, torch.float32, DEV)
+        assert not model.supports_graph
+        assert model.layers[0].feed_forward.router.dtype == torch.float32
+        cache = CacheManager(model.cache_needs(), 2, 128, 16, 10, torch.float32, DEV)
+        runner = ModelRunner(model, cache, torch.float32, DEV, max_tokens=64, max_seqs=2)
+        ids = torch.randint(0, VOCAB, (37,), generator=torch.Generator().manual_seed(2)).tolist()
+        want = plain_routed(w, ids)
+        experts_used = set()
+        cache.assign(0)
+        got, fed = [], 0
+        for count in (9, 2, 16, 1, 1, 1, 7):
+            assert cache.reserve(0, fed + count)
+            logits = runner.step([StepEntry(0, ids[fed:fed + count], fed, list(range(count)))]).logits
+            got.append(logits.double().cpu())
+            fed += count
+            cache.commit(0, fed)
+        mine = torch.cat(got)
+        assert float((mine - want).abs().max() / want.abs().max()) < 1e-4
+        h = plain.rms_norm(w["embed.weight"].double()[torch.tensor(ids)], torch.ones(D_MODEL, dtype=torch.float64), 1e-5)
+        experts_used = set(torch.softmax(h @ w["layers.0.moe.router.weight"].double().T, -1).argmax(-1).tolist())
+        assert len(experts_used) >= 2, "the random router sent every token to one expert: the test shows nothing"
+    finally:
+        unregister_part("feed_forward", "toy_routed")
+        unregister_part("position", "toy_linear_freq")
+        unregister_architecture(RoutedConfig.architecture)
