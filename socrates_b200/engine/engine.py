@@ -44,7 +44,7 @@ def build_model(model_dir, dtype: torch.dtype, device):
     """(configuration, Model with its weights bound) of a model folder."""
     config = load_config(model_dir)
     model = Model(config.plan())
-    tensors = load_weights(model_dir, model.parameters(), dtype, device)
+    tensors = load_weights(model_dir, model.parameters(), dtype, device, model.duplicates())
     model.bind(tensors, dtype)
     return config, model
 

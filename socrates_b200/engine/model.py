@@ -44,6 +44,14 @@ class Model:
                 out[name] = spec
         return out
 
+    def duplicates(self) -> Dict[str, str]:
+        """Tensors a checkpoint may hold beside the one a part reads ({file name: the name it must
+        repeat}); parts say so through an optional `duplicates()`."""
+        out: Dict[str, str] = {}
+        for part in (self.embedding, *self.layers, self.final_norm, self.head):
+            out.update(getattr(part, "duplicates", dict)())
+        return out
+
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype) -> None:
         self.dtype = dtype
         for part in (self.embedding, *self.layers, self.final_norm, self.head):

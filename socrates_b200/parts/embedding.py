@@ -49,6 +49,10 @@ class LMHead(Part):
             return {self.tied_to: ParamSpec((self.vocab, self.hidden))}
         return {self.name + "weight": ParamSpec((self.vocab, self.hidden))}
 
+    def duplicates(self) -> Dict[str, str]:
+        """A tied head reads the embedding; a file may still carry a copy under the head's name."""
+        return {self.name + "weight": self.tied_to} if self.tied_to is not None else {}
+
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype) -> None:
         self.linear = Linear(tensors[self.tied_to or self.name + "weight"])
 

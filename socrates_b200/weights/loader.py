@@ -56,11 +56,17 @@ def _short(names, limit=12):
 
 
 def load_weights(model_dir, expected: Mapping[str, ParamSpec], dtype: torch.dtype,
-                 device="cuda") -> Dict[str, torch.Tensor]:
+                 device="cuda", duplicates: Mapping[str, str] = {}) -> Dict[str, torch.Tensor]:
     """Tensors named by `expected`, checked and moved to `device`.
 
     `dtype` is the engine's dtype (bfloat16 or float32).  Raises WeightsError naming
     every missing tensor, every tensor no part asked for, and every shape that differs.
+
+    `duplicates` names tensors a file may hold beside the one the model reads: {name in the
+    file: the expected tensor it must repeat}, e.g. `lm_head.weight` beside a tied
+    embedding.  Such a tensor is accepted only if it equals the other bit for bit; a copy
+    that differs is reported with the unexpected tensors, because the file then says
+    something else than config.json about what the model is.
     """
     model_dir = Path(model_dir)
     handles = _open_files(model_dir)
@@ -69,7 +75,18 @@ def load_weights(model_dir, expected: Mapping[str, ParamSpec], dtype: torch.dtyp
         for k in h.keys():
             where[k] = h
     missing = [n for n in expected if n not in where]
-    unexpected = [n for n in where if n not in expected]
+    unexpected = []
+    for n in where:
+        if n in expected:
+            continue
+        same_as = duplicates.get(n)
+        if same_as in where and same_as in expected:
+            a, b = where[n].get_tensor(n), where[same_as].get_tensor(same_as)
+            if a.shape == b.shape and a.dtype == b.dtype and torch.equal(a, b):
+                continue                                    # a faithful copy: nothing to read from it
+            unexpected.append(f"{n} (differs from {same_as}, which it should repeat)")
+        else:
+            unexpected.append(n)
     wrong_shape, wrong_dtype = [], []
     for n, spec in expected.items():
         if n in where:

@@ -96,3 +96,27 @@ def test_sharded_folder_with_index(tmp_path):
     (folder / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wm}))
     w = load_weights(folder, expected(TINY_A), torch.bfloat16, "cpu")
     assert set(w) == set(names)
+
+
+def test_copy_of_a_tied_head_is_accepted_only_if_faithful(tmp_path):
+    """A tied configuration whose file also carries lm_head.weight: accepted when it repeats
+    the embedding bit for bit, reported when it differs (the file and config.json would then
+    disagree about what the head is)."""
+    from socrates_b200.config import config_from_dict
+    from socrates_b200.engine.model import Model
+    folder = make_folder(tmp_path, "A")
+    model = Model(config_from_dict(TINY_A).plan())
+    assert model.duplicates() == {"lm_head.weight": "model.embed_tokens.weight"}
+    t = load_file(str(folder / "model.safetensors"))
+    t["lm_head.weight"] = t["model.embed_tokens.weight"].clone()
+    save_file(t, str(folder / "model.safetensors"))
+    w = load_weights(folder, model.parameters(), torch.bfloat16, "cpu", model.duplicates())
+    assert "lm_head.weight" not in w and "model.embed_tokens.weight" in w
+    t["lm_head.weight"][3, 5] += 1
+    save_file(t, str(folder / "model.safetensors"))
+    with pytest.raises(WeightsError) as e:
+        load_weights(folder, model.parameters(), torch.bfloat16, "cpu", model.duplicates())
+    assert len(e.value.unexpected) == 1 and "differs from model.embed_tokens.weight" in e.value.unexpected[0]
+    # an untied configuration declares no such copy
+    from tiny_configs import TINY_B
+    assert Model(config_from_dict(TINY_B).plan()).duplicates() == {}
