@@ -17,6 +17,17 @@ import torch
 from ..kernels import ops
 
 
+def _paged_partition() -> Optional[int]:
+    """PAGED_PARTITION: None for "auto" (or unset), else keys per attention partition (0: no split)."""
+    v = os.environ.get("PAGED_PARTITION", "auto").strip().lower()
+    if v in ("", "auto"):
+        return None
+    n = int(v)
+    if n < 0:
+        raise ValueError(f"PAGED_PARTITION must be 'auto' or a non-negative integer, not {v!r}")
+    return n
+
+
 def _l2_prefetch_budget() -> int:
     """Bytes of the next product's weights that a weight-streaming product asks for in L2 once
     its own loads are issued (`SOCRATES_L2_PREFETCH_MB`, 0 turns it off).  Measured on the 4B
@@ -165,9 +176,14 @@ class StepContext:
         wave, no tail), at most 16, never less than `keys_per_part` keys of the longest
         possible row in a partition.
         """
+        most = max(1, -(-self.max_context // keys_per_part))
+        fixed = _paged_partition()
+        if fixed is not None:
+            # PAGED_PARTITION as in the reference (model/kernels/__init__.py:23-41): keys per
+            # partition, 0 = one pass over all keys; "auto" or unset = the rule below
+            return 1 if fixed == 0 else max(1, min(-(-self.max_context // fixed), 64))
         blocks = max(1, num_kv_heads * self.num_tokens)
         want = (self.num_sms * blocks_per_sm) // blocks
-        most = max(1, -(-self.max_context // keys_per_part))
         return max(1, min(want, most, 16))
 
     def attention(self, out, q, k_pool, v_pool, table, num_heads: int, scale: float, window: int) -> None:

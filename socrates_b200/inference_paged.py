@@ -19,6 +19,10 @@ are overridden by the flags:
                                                              model/inference_cont.py:43
     KV_BLOCK         slots per page, default 16              model/inference_paged.py:51
     ENGINE           only "paged" exists here                model/server.py:79-85
+    ATTN_IMPL        auto or cuda (there also ref, the PyTorch fallback: refused here, there is
+                     no path beside the CUDA kernels)        model/kernels/__init__.py:23-35
+    PAGED_PARTITION  auto, or keys per partition of the split-key decode attention, 0 = one
+                     pass                                    model/kernels/__init__.py:36-41
     MAX_BATCH, MAX_LEN, MAX_NEW_TOKENS   the reference's module constants
                                                              model/inference_cont.py:21-23
 
@@ -67,6 +71,10 @@ def main(argv=None) -> int:
 
     if os.environ.get("ENGINE", "paged") != "paged":
         print(f"ENGINE={os.environ['ENGINE']!r}: only the paged engine exists here", file=sys.stderr)
+        return 2
+    if os.environ.get("ATTN_IMPL", "auto") not in ("auto", "cuda"):
+        print(f"ATTN_IMPL={os.environ['ATTN_IMPL']!r}: this engine has the CUDA kernels only (auto or cuda)",
+              file=sys.stderr)
         return 2
 
     import torch
