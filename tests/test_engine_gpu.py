@@ -135,6 +135,35 @@ def test_running_ahead_changes_nothing(tmp_path, temperature):
     assert n >= 20 and outs[True][2][:n] == outs[False][2][:n]
 
 
+def test_running_ahead_and_stop_tokens(tmp_path):
+    """A stop token ends a request one step after the engine has already launched that request's
+    next step: the early step is dropped and nothing of it shows."""
+    import json
+    from socrates_b200.config import config_from_dict
+    from socrates_b200.weights import write_model_folder
+    from tiny_configs import TINY_A
+    free = engine_for(make_folder(tmp_path / "free", "A"), "float32", max_batch=3, max_new_tokens=40)
+    ps = prompts_for("A", [6, 19, 11])
+    outs = free.generate(ps, max_new_tokens=40, temperature=0.9, seed=21)
+    # a token that some request first produces well into its decoding
+    late = [(o.index(t), t) for o in outs for t in set(o) if o.index(t) >= 5]
+    assert late, "every token of every output appears within the first five: choose other prompts"
+    stop = min(late)[1]
+    folder = write_model_folder(config_from_dict(dict(TINY_A, eos_token_id=stop)), 0, tmp_path / "stop")
+    assert json.loads((folder / "config.json").read_text())["eos_token_id"] == stop
+    got = {}
+    for ahead in (False, True):
+        eng = engine_for(folder, "float32", max_batch=3, max_new_tokens=40, run_ahead=ahead)
+        got[ahead] = eng.generate(ps, max_new_tokens=40, temperature=0.9, seed=21)
+        for want, have in zip(outs, got[ahead]):
+            cut = want.index(stop) if stop in want else len(want)
+            assert have == want[:cut]                    # the stop token itself is not appended
+        assert eng.cache.free_pages() == [g.allocator.num_pages for g in eng.cache.groups]
+        if ahead:
+            assert eng.ahead_discarded >= 1
+    assert got[True] == got[False] and any(len(g) < 40 for g in got[True])
+
+
 def test_few_pages_preemption_keeps_outputs(tmp_path):
     """A pool too small for all requests at once: some are preempted and recomputed, and
     every request still gets the tokens it gets when it runs alone."""
