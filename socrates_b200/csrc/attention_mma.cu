@@ -525,29 +525,32 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         const uint32_t ml_addr = static_cast<uint32_t>(__cvta_generic_to_shared(&c_ml[0][0]));
         for (int idx = part * NTHR + threadIdx.x; idx < G * D; idx += NP * NTHR) {
             const int row = idx / D;
-            float M = -INFINITY;
-            for (int p = 0; p < NP; ++p) {
-                uint32_t a;
-                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(ml_addr + row * 8), "r"(p));
-                float m, l;
-                asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(m), "=f"(l) : "r"(a) : "memory");
-                if (l > 0.f) M = fmaxf(M, m);
-            }
-            float L = 0.f, o = 0.f;
-            for (int p = 0; p < NP; ++p) {
-                uint32_t a, b;
-                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(ml_addr + row * 8), "r"(p));
-                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(b) : "r"(co_addr + idx * 4), "r"(p));
-                float m, l;
-                asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(m), "=f"(l) : "r"(a) : "memory");
-                if (l > 0.f) {
-                    float v;
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(b) : "memory");
-                    const float f = expf(m - M);
-                    L += f * l;
-                    o += f * v;
+            // every partition's (max, sum) and value first (NP <= 4: all loads in flight at once; an
+            // empty partition's value is whatever its shared memory holds and is not used), then the sum
+            float pm[4], pl[4], pv[4];
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                pm[p] = -INFINITY; pl[p] = 0.f; pv[p] = 0.f;
+                if (p < NP) {
+                    uint32_t a, b;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(ml_addr + row * 8), "r"(p));
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(b) : "r"(co_addr + idx * 4), "r"(p));
+                    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(pm[p]), "=f"(pl[p]) : "r"(a) : "memory");
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv[p]) : "r"(b) : "memory");
                 }
             }
+            float M = -INFINITY;
+#pragma unroll
+            for (int p = 0; p < 4; ++p)
+                if (pl[p] > 0.f) M = fmaxf(M, pm[p]);
+            float L = 0.f, o = 0.f;
+#pragma unroll
+            for (int p = 0; p < 4; ++p)
+                if (pl[p] > 0.f) {
+                    const float f = expf(pm[p] - M);
+                    L += f * pl[p];
+                    o += f * pv[p];
+                }
             out[((size_t)n * Hq + h0 + row) * D + (idx - row * D)] = __float2bfloat16_rn(o / L);
         }
         // nobody leaves while another block may still read its shared memory

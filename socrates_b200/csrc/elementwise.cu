@@ -104,44 +104,40 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
 // The same with 16-byte accesses (d a multiple of 4, 16-byte aligned rows): each thread
 // owns whole float4 columns, the S partial sums of a column are loaded back to back
 // (independent loads) and added in the fixed order s = 0, 1, ...
+// At most 640 threads a block: sixteen float4 loads in flight need about a hundred registers.
 template <typename T>
-__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ delta,
+__global__ void __launch_bounds__(640) add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ delta,
                                        int S, size_t delta_stride, const float* __restrict__ gain,
                                        T* __restrict__ out, const int* __restrict__ row_index, int d,
                                        float eps, int write_residual) {
     sb::pdl_launch_dependents();     // the next kernel may begin its prologue
-    sb::pdl_wait();                  // everything before this kernel is complete and visible
     extern __shared__ float row[];          // d floats
     __shared__ float scratch[33];
     const int m = blockIdx.x;
+    const int d4 = d / 4;
+    // The gain is a weight (nobody writes it): a thread's first column of it is fetched before
+    // the wait on the preceding kernel instead of after the reduction.
+    const float4* gain4 = reinterpret_cast<const float4*>(gain);
+    const float4 g_first = threadIdx.x < d4 ? __ldg(gain4 + threadIdx.x) : make_float4(0.f, 0.f, 0.f, 0.f);
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
     const int r = row_index ? row_index[m] : m;
     float4* res4 = reinterpret_cast<float4*>(residual + (size_t)r * d);
     const float4* del4 = reinterpret_cast<const float4*>(delta + (size_t)r * d);
     const size_t stride4 = delta_stride / 4;
     float4* row4 = reinterpret_cast<float4*>(row);
-    const int d4 = d / 4;
     float ss = 0.f;
     for (int i = threadIdx.x; i < d4; i += blockDim.x) {
         float4 v = res4[i];
-        int s = 0;
-        for (; s + 8 <= S; s += 8) {                 // eight independent loads in flight, added in order
-            float4 p[8];
+        // up to sixteen partial sums' loads in flight at once (one round trip for the 13 or 14
+        // parts of a decode step's narrow projections), added in the order s = 0, 1, ...
+        for (int s0 = 0; s0 < S; s0 += 16) {
+            float4 p[16];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) p[j] = __ldg(del4 + (s + j) * stride4 + i);
+            for (int j = 0; j < 16; ++j)
+                if (s0 + j < S) p[j] = __ldg(del4 + (size_t)(s0 + j) * stride4 + i);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) { v.x += p[j].x; v.y += p[j].y; v.z += p[j].z; v.w += p[j].w; }
-        }
-        for (; s + 4 <= S; s += 4) {
-            const float4 a = __ldg(del4 + (s + 0) * stride4 + i), b = __ldg(del4 + (s + 1) * stride4 + i);
-            const float4 c = __ldg(del4 + (s + 2) * stride4 + i), e = __ldg(del4 + (s + 3) * stride4 + i);
-            v.x = ((((v.x + a.x) + b.x) + c.x) + e.x);
-            v.y = ((((v.y + a.y) + b.y) + c.y) + e.y);
-            v.z = ((((v.z + a.z) + b.z) + c.z) + e.z);
-            v.w = ((((v.w + a.w) + b.w) + c.w) + e.w);
-        }
-        for (; s < S; ++s) {
-            const float4 a = __ldg(del4 + s * stride4 + i);
-            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            for (int j = 0; j < 16; ++j)
+                if (s0 + j < S) { v.x += p[j].x; v.y += p[j].y; v.z += p[j].z; v.w += p[j].w; }
         }
         row4[i] = v;
         if (write_residual) res4[i] = v;
@@ -149,10 +145,9 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const float
     }
     const float total = block_sum(ss, scratch);
     const float rinv = 1.0f / sqrtf(total / (float)d + eps);
-    const float4* gain4 = reinterpret_cast<const float4*>(gain);
     T* o = out + (size_t)m * d;
     for (int i = threadIdx.x; i < d4; i += blockDim.x) {
-        const float4 v = row4[i], g = __ldg(gain4 + i);
+        const float4 v = row4[i], g = i == (int)threadIdx.x ? g_first : __ldg(gain4 + i);
         const float a = v.x * rinv * g.x, b = v.y * rinv * g.y, c = v.z * rinv * g.z, e = v.w * rinv * g.w;
         if constexpr (sizeof(T) == 2) {
             __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, e);
@@ -183,7 +178,7 @@ extern "C" int sb_add_rmsnorm(float* residual, const float* delta, int S, long l
     int threads = d >= 2048 ? 512 : 256;
     if (vec) {
         threads = ((d / 4 + 31) / 32) * 32;
-        if (threads > 1024) threads = 1024;
+        if (threads > 640) threads = 640;
         if (M > 512 && threads > 256) threads = 256;
     }
 #define SB_NORM_LAUNCH(KERNEL, T)                                                                        \
@@ -313,8 +308,20 @@ __global__ void qk_norm_rope_kvwrite_fast_kernel(
             sn[j] = sinf(ang);
         }
     }
-    // positions and inv_freq are older than the preceding kernel (a host copy, a constant
-    // table), so the trigonometry above overlaps that kernel's tail.
+    // positions, rows and the block table are older than the preceding kernel (a host copy),
+    // inv_freq and the gains are weights: the trigonometry above, the page of this token's key
+    // and value, and this lane's gains are all there before that kernel has finished.
+    size_t kv_slot = 0;
+    if (write_kv) {
+        const int page = block_table[(size_t)token_rows[n] * table_width + pos / BS];
+        kv_slot = ((size_t)page * Hkv * BS + (pos % BS)) * D;            // + kh * BS * D per KV head
+    }
+    float gq[VPL], gk[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        gq[i] = q_gain != nullptr ? q_gain[lane * VPL + i] : 1.f;
+        gk[i] = k_gain != nullptr ? k_gain[lane * VPL + i] : 1.f;
+    }
     sb::pdl_wait();                  // everything before this kernel is complete and visible
     __syncthreads();
     const int head_end = min(n_heads, (int)(blockIdx.y + 1) * heads_per_block);
@@ -366,7 +373,7 @@ __global__ void qk_norm_rope_kvwrite_fast_kernel(
                 ss = warp_sum(ss);
                 const float rinv = 1.0f / sqrtf(ss / (float)D + eps);
 #pragma unroll
-                for (int i = 0; i < VPL; ++i) y[u][i] = y[u][i] * rinv * gain[lane * VPL + i];
+                for (int i = 0; i < VPL; ++i) y[u][i] = y[u][i] * rinv * (is_q ? gq[i] : gk[i]);
             }
             Pack<T, VPL> o;
             if (!is_v && R == D) {
@@ -385,10 +392,8 @@ __global__ void qk_norm_rope_kvwrite_fast_kernel(
                 dst = q_out + ((size_t)n * Hq + head) * D;
             } else {
                 const int kh = is_k ? head - Hq : head - Hq - Hkv;
-                const int row = token_rows[n];
-                const int page = block_table[(size_t)row * table_width + pos / BS];
                 T* pool = is_k ? k_pool : v_pool;
-                dst = pool + (((size_t)page * Hkv + kh) * BS + (pos % BS)) * D;
+                dst = pool + kv_slot + (size_t)kh * BS * D;
             }
             *reinterpret_cast<Pack<T, VPL>*>(dst + lane * VPL) = o;
         }

@@ -149,6 +149,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     sb::pdl_launch_dependents();          // the next kernel may begin its prologue
     if (warp == 0 && lane == 0) {
         // ---------------- producer: TMA loads into the ring.
+        // (both tensor maps are fetched now: the activations' map is first used right after the
+        // wait on the previous kernel, where its fetch would be on the step's critical path)
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_b) : "memory");
         // The weight operand (tma_a when SWAP, else tma_b) is written by no kernel, so its
         // tiles of the first ring-full of stages are fetched BEFORE the wait on the previous
         // kernel; the activation tiles of those stages follow after it.
