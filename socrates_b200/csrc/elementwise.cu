@@ -104,9 +104,11 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
 // The same with 16-byte accesses (d a multiple of 4, 16-byte aligned rows): each thread
 // owns whole float4 columns, the S partial sums of a column are loaded back to back
 // (independent loads) and added in the fixed order s = 0, 1, ...
-// At most 640 threads a block: sixteen float4 loads in flight need about a hundred registers.
-template <typename T>
-__global__ void __launch_bounds__(640) add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ delta,
+// DEPTH partial sums' loads are in flight at once: 16 for the few rows of a decode step (one round
+// trip for the 13 or 14 parts of its narrow projections; about a hundred registers, so at most
+// 640 threads a block), 2 for many rows, where the rows themselves keep memory busy.
+template <typename T, int DEPTH>
+__global__ void __launch_bounds__(DEPTH > 8 ? 640 : 1024) add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ delta,
                                        int S, size_t delta_stride, const float* __restrict__ gain,
                                        T* __restrict__ out, const int* __restrict__ row_index, int d,
                                        float eps, int write_residual) {
@@ -128,15 +130,14 @@ __global__ void __launch_bounds__(640) add_rmsnorm_vec_kernel(float* __restrict_
     float ss = 0.f;
     for (int i = threadIdx.x; i < d4; i += blockDim.x) {
         float4 v = res4[i];
-        // up to sixteen partial sums' loads in flight at once (one round trip for the 13 or 14
-        // parts of a decode step's narrow projections), added in the order s = 0, 1, ...
-        for (int s0 = 0; s0 < S; s0 += 16) {
-            float4 p[16];
+        // DEPTH loads in flight, added in the order s = 0, 1, ...
+        for (int s0 = 0; s0 < S; s0 += DEPTH) {
+            float4 p[DEPTH];
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
+            for (int j = 0; j < DEPTH; ++j)
                 if (s0 + j < S) p[j] = __ldg(del4 + (size_t)(s0 + j) * stride4 + i);
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
+            for (int j = 0; j < DEPTH; ++j)
                 if (s0 + j < S) { v.x += p[j].x; v.y += p[j].y; v.z += p[j].z; v.w += p[j].w; }
         }
         row4[i] = v;
@@ -161,6 +162,9 @@ __global__ void __launch_bounds__(640) add_rmsnorm_vec_kernel(float* __restrict_
     }
 }
 
+// the output pointer type of a norm kernel instantiation (its first template argument)
+template <typename T, int DEPTH = 0> T* sb_out_type();
+
 extern "C" int sb_add_rmsnorm(float* residual, const float* delta, int S, long long delta_stride,
                               const float* gain, void* out, const int* row_index, int M, int d,
                               float eps, int dtype, cudaStream_t stream) {
@@ -178,21 +182,23 @@ extern "C" int sb_add_rmsnorm(float* residual, const float* delta, int S, long l
     int threads = d >= 2048 ? 512 : 256;
     if (vec) {
         threads = ((d / 4 + 31) / 32) * 32;
-        if (threads > 640) threads = 640;
+        if (threads > (M <= 64 ? 640 : 1024)) threads = M <= 64 ? 640 : 1024;
         if (M > 512 && threads > 256) threads = 256;
     }
-#define SB_NORM_LAUNCH(KERNEL, T)                                                                        \
+#define SB_NORM_LAUNCH(KERNEL, ...)                                                                      \
     do {                                                                                                  \
         if (smem > 48 * 1024)                                                                             \
-            cudaFuncSetAttribute(KERNEL<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-        sb::launch(KERNEL<T>, dim3(M), dim3(threads), smem, stream, residual, delta, S, (size_t)delta_stride, gain, (T*)out,  \
-                                                row_index, d, eps, write_residual);                      \
+            cudaFuncSetAttribute(KERNEL<__VA_ARGS__>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+        sb::launch(KERNEL<__VA_ARGS__>, dim3(M), dim3(threads), smem, stream, residual, delta, S, (size_t)delta_stride, gain, \
+                   (decltype(sb_out_type<__VA_ARGS__>()))out, row_index, d, eps, write_residual);        \
     } while (0)
     if (dtype == SB_F32) {
-        if (vec) SB_NORM_LAUNCH(add_rmsnorm_vec_kernel, float);
+        if (vec && M <= 64) SB_NORM_LAUNCH(add_rmsnorm_vec_kernel, float, 16);
+        else if (vec) SB_NORM_LAUNCH(add_rmsnorm_vec_kernel, float, 2);
         else SB_NORM_LAUNCH(add_rmsnorm_kernel, float);
     } else if (dtype == SB_BF16) {
-        if (vec) SB_NORM_LAUNCH(add_rmsnorm_vec_kernel, __nv_bfloat16);
+        if (vec && M <= 64) SB_NORM_LAUNCH(add_rmsnorm_vec_kernel, __nv_bfloat16, 16);
+        else if (vec) SB_NORM_LAUNCH(add_rmsnorm_vec_kernel, __nv_bfloat16, 2);
         else SB_NORM_LAUNCH(add_rmsnorm_kernel, __nv_bfloat16);
     } else {
         SB_REQUIRE(false, "add_rmsnorm: unknown dtype %d", dtype);
@@ -286,7 +292,7 @@ template <typename T, int VPL> struct alignas(sizeof(T) * VPL) Pack { T v[VPL]; 
 // finds its rotation partner (dim +- D/2) in lane l ^ 16.  A block serves `heads_per_block`
 // heads of one token; its first D/2 threads compute the token's cosines and sines once
 // into shared memory, so the trigonometry is not repeated for every head.
-template <typename T, int VPL, int U>
+template <typename T, int VPL, bool EARLY>
 __global__ void qk_norm_rope_kvwrite_fast_kernel(
     const T* __restrict__ qkv, const float* __restrict__ parts, int S, size_t part_stride,
     T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool,
@@ -311,22 +317,27 @@ __global__ void qk_norm_rope_kvwrite_fast_kernel(
     // positions, rows and the block table are older than the preceding kernel (a host copy),
     // inv_freq and the gains are weights: the trigonometry above, the page of this token's key
     // and value, and this lane's gains are all there before that kernel has finished.
+    // (EARLY: the few blocks of a decode step, where every round trip after the wait counts; with
+    // many tokens the registers this takes would cost a resident block per SM, and the rows
+    // themselves hide the latency)
     size_t kv_slot = 0;
-    if (write_kv) {
-        const int page = block_table[(size_t)token_rows[n] * table_width + pos / BS];
-        kv_slot = ((size_t)page * Hkv * BS + (pos % BS)) * D;            // + kh * BS * D per KV head
-    }
     float gq[VPL], gk[VPL];
+    if (EARLY) {
+        if (write_kv) {
+            const int page = block_table[(size_t)token_rows[n] * table_width + pos / BS];
+            kv_slot = ((size_t)page * Hkv * BS + (pos % BS)) * D;        // + kh * BS * D per KV head
+        }
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) {
-        gq[i] = q_gain != nullptr ? q_gain[lane * VPL + i] : 1.f;
-        gk[i] = k_gain != nullptr ? k_gain[lane * VPL + i] : 1.f;
+        for (int i = 0; i < VPL; ++i) {
+            gq[i] = q_gain != nullptr ? q_gain[lane * VPL + i] : 1.f;
+            gk[i] = k_gain != nullptr ? k_gain[lane * VPL + i] : 1.f;
+        }
     }
     sb::pdl_wait();                  // everything before this kernel is complete and visible
     __syncthreads();
     const int head_end = min(n_heads, (int)(blockIdx.y + 1) * heads_per_block);
     const int nwarps = blockDim.x >> 5;
-    // U = heads whose loads a warp has in flight at once
+    constexpr int U = 1;             // heads whose loads a warp has in flight at once (4 was measured slower)
     for (int head0 = blockIdx.y * heads_per_block + warp; head0 < head_end; head0 += U * nwarps) {
         float y[U][VPL];
 #pragma unroll
@@ -373,7 +384,8 @@ __global__ void qk_norm_rope_kvwrite_fast_kernel(
                 ss = warp_sum(ss);
                 const float rinv = 1.0f / sqrtf(ss / (float)D + eps);
 #pragma unroll
-                for (int i = 0; i < VPL; ++i) y[u][i] = y[u][i] * rinv * (is_q ? gq[i] : gk[i]);
+                for (int i = 0; i < VPL; ++i)
+                    y[u][i] = y[u][i] * rinv * (EARLY ? (is_q ? gq[i] : gk[i]) : gain[lane * VPL + i]);
             }
             Pack<T, VPL> o;
             if (!is_v && R == D) {
@@ -393,6 +405,10 @@ __global__ void qk_norm_rope_kvwrite_fast_kernel(
             } else {
                 const int kh = is_k ? head - Hq : head - Hq - Hkv;
                 T* pool = is_k ? k_pool : v_pool;
+                if (!EARLY) {
+                    const int page = block_table[(size_t)token_rows[n] * table_width + pos / BS];
+                    kv_slot = ((size_t)page * Hkv * BS + (pos % BS)) * D;
+                }
                 dst = pool + kv_slot + (size_t)kh * BS * D;
             }
             *reinterpret_cast<Pack<T, VPL>*>(dst + lane * VPL) = o;
@@ -423,7 +439,8 @@ static void qk_launch(const void* qkv, const float* parts, int S, size_t part_st
     // (Four heads' loads in flight per warp, U = 4, were measured slower for prompt portions:
     // 35.5 against 29.0 us for 2,048 tokens of the 4B shape.)
 #define SB_QK_FAST(VPL_) \
-    sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, VPL_, 1>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb);
+    if (hpb > 4) sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, VPL_, false>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb); \
+    else sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, VPL_, true>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb);
     if (fast && D == 64) { SB_QK_FAST(2) }
     else if (fast && D == 128) { SB_QK_FAST(4) }
     else if (fast) { SB_QK_FAST(8) }
