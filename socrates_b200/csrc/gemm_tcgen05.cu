@@ -18,6 +18,7 @@
 // (again bounded) for its own copies in flight, frees its tensor memory and returns.
 #include <cuda.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -107,11 +108,25 @@ namespace {
 // tma_b: the operand whose rows become accumulator columns, [rows_b, K], box {64, BN}.
 // SWAP = false: lanes are rows of C (m), columns are columns of C (n).
 // SWAP = true : lanes are columns of C (n), columns are rows of C (m).
+//
+// A thread issues a tcgen05.mma about every 80 ns however narrow the tile, which for the narrow
+// tiles of weight streaming is longer than the tile's loads take.  With SWAP, `issuers` (1 to
+// kMaxIssuers) threads therefore share the issuing, each into an accumulator of its own, and the
+// epilogue adds the accumulators.  A ring stage always belongs to the same thread (stage s to
+// thread s mod issuers): a thread that met only some of a stage's uses could not tell, from the
+// parity it waits for, a stage that has been refilled from one that has not been filled yet.
+constexpr int kMaxIssuers = 3;
+constexpr int kDefaultIssuers = 2;      // measured: 2.58 ms a decode step against 2.62 (one) and 2.59 (three)
+template <int BN, bool SWAP> constexpr int acc_cols() {
+    constexpr int want = (SWAP ? kMaxIssuers : 1) * BN;
+    return want <= 32 ? 32 : want <= 64 ? 64 : want <= 128 ? 128 : want <= 256 ? 256 : 512;
+}
+
 template <int BN, int STAGES, bool SWAP, typename TC, int EPI = 0>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 2)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     TC* __restrict__ C, int M, int N, int K, int kb_per_split, int* __restrict__ status,
-                    const uint8_t* __restrict__ next_w, long long next_bytes) {
+                    const uint8_t* __restrict__ next_w, long long next_bytes, int issuers) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[STAGES];
     __shared__ __align__(8) uint64_t empty_bar[STAGES];
@@ -126,19 +141,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const int kb_begin = blockIdx.z * kb_per_split;
     const int kb_end = min(kb_total, kb_begin + kb_per_split);
     const int kb_count = kb_end - kb_begin;
+    if (!SWAP) issuers = 1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
-        mbar_init(smem_u32(&accum_bar), 1);
+        mbar_init(smem_u32(&accum_bar), issuers);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&tmem_base_slot)), "r"(tmem_cols<BN>()) : "memory");
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(acc_cols<BN, SWAP>()) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tcgen05_fence_before();
@@ -206,13 +222,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 l2_prefetch(next_w + off, (uint32_t)(left < kL2Chunk ? left : kL2Chunk));
             }
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---------------- MMA issuer
+    } else if (warp >= 1 && warp <= issuers && lane == 0) {
+        // ---------------- MMA issuer q of `issuers`: the K blocks of its stages into accumulator q
         constexpr uint32_t idesc = make_idesc(BN);
-        bool ok = true;
+        const int q = warp - 1;
+        const uint32_t acc = tmem_d + q * BN;
+        bool ok = true, first = true;
+        // s, owner and parity follow i % STAGES, s % issuers and (i / STAGES) & 1 without dividing
+        int s = -1, owner = -1;
+        uint32_t parity = 0;
         for (int i = 0; i < kb_count && ok; ++i) {
-            const int s = i % STAGES;
-            if (!mbar_wait(smem_u32(&full_bar[s]), (i / STAGES) & 1)) {
+            if (++owner == issuers) owner = 0;
+            if (++s == STAGES) { s = 0; owner = 0; parity ^= (i > 0); }
+            if (owner != q) continue;
+            if (!mbar_wait(smem_u32(&full_bar[s]), parity)) {
                 atomicExch(status, 2);
                 atomicExch(&abort_flag, 1);
                 ok = false;
@@ -225,11 +248,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             for (int k = 0; k < BK / UMMA_K; ++k) {
                 const uint64_t da = make_smem_desc(sa + k * UMMA_K * 2);
                 const uint64_t db = make_smem_desc(sb + k * UMMA_K * 2);
-                tcgen05_mma_bf16(tmem_d, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                tcgen05_mma_bf16(acc, da, db, idesc, (!first || k > 0) ? 1u : 0u);
             }
+            first = false;
             tcgen05_commit(smem_u32(&empty_bar[s]));   // frees the stage when these MMAs have read it
         }
-        tcgen05_commit(smem_u32(&accum_bar));          // arrives when every MMA above has completed
+        tcgen05_commit(smem_u32(&accum_bar));          // arrives when every MMA of this thread has completed
     }
     __syncwarp();
 
@@ -246,8 +270,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 #pragma unroll
         for (int c0 = 0; c0 < BN; c0 += 16) {
             uint32_t r[16];
-            tmem_ld16(tmem_d + (static_cast<uint32_t>(warp * 32) << 16) + c0, r);
-            tmem_ld_wait();
+            const uint32_t at = tmem_d + (static_cast<uint32_t>(warp * 32) << 16) + c0;
+            tmem_ld16(at, r);
+            if constexpr (SWAP) {
+                // the accumulators of the other issuing threads count where those had a K block
+                // (all are read, so that the loads overlap; what an unused one holds is dropped)
+                const int used = min(issuers, kb_count);
+                uint32_t r1[16], r2[16];
+                tmem_ld16(at + BN, r1);
+                tmem_ld16(at + 2 * BN, r2);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float v1 = used > 1 ? __uint_as_float(r1[j]) : 0.0f;
+                    const float v2 = used > 2 ? __uint_as_float(r2[j]) : 0.0f;
+                    r[j] = __float_as_uint(__uint_as_float(r[j]) + v1 + v2);
+                }
+            } else {
+                tmem_ld_wait();
+            }
             if (SWAP && EPI == 1) {
                 // weight rows interleave gate and up: lane pairs (even = gate_f, odd = up_f);
                 // the even lane writes C[m, f] = up * silu(gate), C has N/2 columns
@@ -304,7 +345,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols<BN>())
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(acc_cols<BN, SWAP>())
                      : "memory");
     }
 }
@@ -316,6 +357,16 @@ using sb::get_map;
 // the duration of one dispatch; the weight-streaming kernel passes them on).
 struct NextWeights { const uint8_t* ptr = nullptr; long long bytes = 0; };
 thread_local NextWeights g_next;
+
+// How many threads issue the MMAs of a weight-streaming block (SOCRATES_GEMM_ISSUERS, 1 to 3).
+int issuing_threads() {
+    static const int n = [] {
+        const char* e = getenv("SOCRATES_GEMM_ISSUERS");
+        const int v = e ? atoi(e) : kDefaultIssuers;
+        return v < 1 ? 1 : (v > kMaxIssuers ? kMaxIssuers : v);
+    }();
+    return n;
+}
 
 template <int BN, int STAGES, bool SWAP, typename TC, int EPI = 0>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, int K, dim3 grid, int kb_per_split,
@@ -330,7 +381,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, 
     }
     const NextWeights next = SWAP ? g_next : NextWeights{};
     sb::launch(kernel, dim3(grid), dim3(128), smem, stream, ma, mb, (TC*)C, M, N, K, kb_per_split, status,
-               next.ptr, next.bytes);
+               next.ptr, next.bytes, issuing_threads());
     return 0;
 }
 

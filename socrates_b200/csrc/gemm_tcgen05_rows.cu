@@ -23,7 +23,7 @@ namespace {
 constexpr int ACC_STRIDE = 256;          // TMEM columns between the two accumulators
 
 template <int BN, int STAGES, typename TC, int EPI>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                                TC* __restrict__ C, int M, int N, int K, int tiles_m, int tiles_n,
                                int* __restrict__ status) {
@@ -262,7 +262,7 @@ __host__ __device__ constexpr uint32_t make_idesc_pair(int bn) {
 template <int BN> constexpr int pair_stage_bytes() { return BM * BK * 2 + (BN / 2) * BK * 2; }
 
 template <int BN, int STAGES, typename TC, int EPI>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                          TC* __restrict__ C, int M, int N, int K, int tiles_m, int tiles_n,
                          int* __restrict__ status) {

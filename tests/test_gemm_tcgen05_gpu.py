@@ -65,6 +65,23 @@ def test_gemm_tcgen05_split_k(ops, M, N, K, splits):
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("M", [3, 24, 50])
+def test_gemm_tcgen05_few_rows_long_k(ops, M):
+    """K so long that the ring of stages is refilled dozens of times, in each of the three tile
+    widths for few rows: the threads that share the issuing of the MMAs must each meet their
+    stages' refills in order.  Launched back to back many times, one result for all."""
+    N, K = 640, 17408
+    a, w, want = operands(M, N, K, seed=2)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    outs = [torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV) for _ in range(40)]
+    for out in outs:
+        ops.gemm_tcgen05(out, a, w, status)
+    close(outs[0], want, K, False)
+    for out in outs[1:]:
+        assert torch.equal(out, outs[0])
+    assert int(status.item()) == 0
+
+
 def test_gemm_tcgen05_one_hot_rows_and_columns(ops):
     """Operands that are rows of the identity: the product must reproduce the other
     operand exactly, which shows a transposed, shifted or swizzle-scrambled tile."""
