@@ -215,7 +215,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
     const int G = Hq / Hkv;
     const int bs_log2 = 31 - __clz(BS);
     const int TQ = ROWS / G;
-    const int kh = blockIdx.y;
+    const int kh = blockIdx.x % Hkv;          // the KV heads of a query tile are neighbours in launch order
 
     if (tid == 0) {
         for (int b = 0; b < 2; ++b) {
@@ -238,9 +238,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
     sb::pdl_wait();                                        // q and the pages are written by earlier kernels
 
     // ---- which request, which tile.  Blocks are handed out in launch order and later tiles of
-    // a prompt have more keys, so the order is reversed: the longest tiles start first and the
-    // short ones fill the tail.
-    int tile = gridDim.x - 1 - blockIdx.x, r = 0, t0 = 0, n_tok = 0;
+    // a prompt have more keys, so the order is reversed: the longest tiles (of every KV head) start
+    // first and the short ones fill the tail.  With the KV head as the slow index instead, the
+    // longest tiles of the last heads started when half of the SMs had nothing else left: 93 us
+    // against 66 for one prompt of 2,048 tokens.
+    int tile = gridDim.x / Hkv - 1 - blockIdx.x / Hkv, r = 0, t0 = 0, n_tok = 0;
     for (; r < R; ++r) {
         const int a = seq_starts[r], len = seq_starts[r + 1] - a;
         const int tiles = (len + TQ - 1) / TQ;
@@ -571,7 +573,7 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, void* out, const void* 
         configured = true;
     }
     const int TQ = ROWS / (Hq / Hkv);
-    dim3 grid(N / TQ + R, Hkv);                              // an upper bound of the number of tiles
+    dim3 grid((N / TQ + R) * Hkv);                           // an upper bound of the number of tiles, times heads
     sb::launch(kernel, grid, dim3(THREADS), smem_bytes<D>() + table_width * 4, stream, mk, mv, (bf16*)out,
                (const bf16*)q, block_table, table_width, seq_starts, seq_rows, seq_first_pos, R, Hq, Hkv, BS, window,
                scale * LOG2E, status);
