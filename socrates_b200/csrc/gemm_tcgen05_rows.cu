@@ -20,10 +20,18 @@ namespace {
 //   EPI = 0: C[m, n] = acc
 //   EPI = 1: the weight rows interleave gate and up (row 2f = gate_f, row 2f+1 = up_f);
 //            C[m, f] = up * silu(gate), C has N/2 columns (SiLU*mul fused into the product).
+//
+// ISSUERS = 2 (tile widths below 256, where one thread's rate of about one product every 80 ns,
+// not the tensor core, sets the pace): a seventh warp issues too.  Each of the two threads issues
+// half of every K block's products into an accumulator of its own (columns BN.. beside the
+// first), and the epilogue adds the two.  Where four such accumulators do not fit into the 512
+// columns, a tile's main loop waits for the epilogue of the tile before it.
 constexpr int ACC_STRIDE = 256;          // TMEM columns between the two accumulators
 
-template <int BN, int STAGES, typename TC, int EPI>
-__global__ void __launch_bounds__(192, 1)
+template <int BN, int ISSUERS> constexpr int acc_buffers() { return 2 * ISSUERS * BN <= 512 ? 2 : 1; }
+
+template <int BN, int STAGES, typename TC, int EPI, int ISSUERS>
+__global__ void __launch_bounds__(160 + 32 * ISSUERS, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                                TC* __restrict__ C, int M, int N, int K, int tiles_m, int tiles_n,
                                int* __restrict__ status) {
@@ -43,10 +51,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 1);
-            mbar_init(smem_u32(&empty_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), ISSUERS);   // one commit per issuing thread
         }
         for (int a = 0; a < 2; ++a) {
-            mbar_init(smem_u32(&acc_full[a]), 1);
+            mbar_init(smem_u32(&acc_full[a]), ISSUERS);
             mbar_init(smem_u32(&acc_empty[a]), 4);      // one arrival per epilogue warp
         }
         abort_flag = 0;
@@ -111,18 +119,21 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const 
             for (uint32_t i = it > STAGES ? it - STAGES : 0; i < it; ++i)
                 mbar_wait(smem_u32(&full_bar[i % STAGES]), (i / STAGES) & 1);
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---------------- MMA issuer
+    } else if ((warp == 1 || warp == 6) && lane == 0) {
+        // ---------------- MMA issuer q (warp 1, and warp 6 when there are two)
         constexpr uint32_t idesc = make_idesc(BN);
+        constexpr int NACC = acc_buffers<BN, ISSUERS>();
+        constexpr int KPER = (BK / UMMA_K) / ISSUERS;      // products of a K block per issuing thread
+        const int q = warp == 1 ? 0 : 1;
         uint32_t it = 0;
         int j = 0;                                         // tiles done by this block
         bool ok = true;
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++j) {
-            const int acc = j & 1;
+            const int acc = j % NACC;
             // the epilogue must have drained this accumulator (first use of each passes at once)
-            if (j >= 2 && !mbar_wait(smem_u32(&acc_empty[acc]), ((j >> 1) - 1) & 1)) { ok = false; break; }
+            if (j >= NACC && !mbar_wait(smem_u32(&acc_empty[acc]), ((j / NACC) - 1) & 1)) { ok = false; break; }
             tcgen05_fence_after();
-            const uint32_t d = tmem_d + acc * ACC_STRIDE;
+            const uint32_t d = tmem_d + acc * ACC_STRIDE + q * BN;
             for (int i = 0; i < kb_total; ++i, ++it) {
                 const int s = it % STAGES;
                 if (!mbar_wait(smem_u32(&full_bar[s]), (it / STAGES) & 1)) { ok = false; break; }
@@ -130,9 +141,9 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const 
                 const uint32_t sa = tiles + s * stage_bytes<BN>();
                 const uint32_t sb_ = sa + BM * BK * 2;
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k)
+                for (int k = q * KPER; k < (q + 1) * KPER; ++k)
                     tcgen05_mma_bf16(d, make_smem_desc(sa + k * UMMA_K * 2), make_smem_desc(sb_ + k * UMMA_K * 2),
-                                     idesc, (i > 0 || k > 0) ? 1u : 0u);
+                                     idesc, (i > 0 || k > q * KPER) ? 1u : 0u);
                 tcgen05_commit(smem_u32(&empty_bar[s]));
             }
             if (!ok) break;
@@ -142,14 +153,15 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const 
             atomicExch(status, 2);
             atomicExch(&abort_flag, 1);
         }
-    } else if (warp >= 2) {
+    } else if (warp >= 2 && warp < 6) {
         // ---------------- epilogue: warp w owns TMEM lanes 32*(w%4) .. +31
         sb::pdl_wait();                                    // C may still be read by an earlier kernel until now
+        constexpr int NACC = acc_buffers<BN, ISSUERS>();
         const int quarter = warp & 3;
         int j = 0;
         for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++j) {
-            const int acc = j & 1;
-            bool good = mbar_wait(smem_u32(&acc_full[acc]), (j >> 1) & 1);
+            const int acc = j % NACC;
+            bool good = mbar_wait(smem_u32(&acc_full[acc]), (j / NACC) & 1);
             if (*((volatile int*)&abort_flag)) good = false;
             good = __all_sync(0xffffffffu, good);
             if (!good) {
@@ -160,7 +172,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const 
             const int a0 = (t % tiles_m) * BM, b0 = (t / tiles_m) * BN;
             const int m = a0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_d + acc * ACC_STRIDE + (static_cast<uint32_t>(quarter * 32) << 16);
-            drain_tile<BN, TC, EPI>(taddr, C, M, N, m, b0);
+            drain_tile<BN, TC, EPI, (ISSUERS == 2 ? BN : 0)>(taddr, C, M, N, m, b0);
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -431,10 +443,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
 
 using sb::get_map;
 
-template <int BN, int STAGES, typename TC, int EPI>
+template <int BN, int STAGES, typename TC, int EPI, int ISSUERS>
 int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, int K, int* status,
                       cudaStream_t stream) {
-    auto kernel = gemm_tcgen05_persistent_kernel<BN, STAGES, TC, EPI>;
+    auto kernel = gemm_tcgen05_persistent_kernel<BN, STAGES, TC, EPI, ISSUERS>;
     constexpr int smem = STAGES * stage_bytes<BN>() + 1024;
     static bool configured = false;
     static int num_sms = 0;
@@ -448,7 +460,8 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int
     }
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
     const int blocks = min(tiles_m * tiles_n, num_sms);
-    sb::launch(kernel, dim3(blocks), dim3(192), smem, stream, ma, mb, (TC*)C, M, N, K, tiles_m, tiles_n, status);
+    sb::launch(kernel, dim3(blocks), dim3(160 + 32 * ISSUERS), smem, stream, ma, mb, (TC*)C, M, N, K, tiles_m, tiles_n,
+               status);
     return 0;
 }
 
@@ -503,20 +516,27 @@ constexpr int persistent_stages(int bn) {
 }
 
 // Tile width for many rows.  Blocks take tiles in a fixed stride, so the time is the number
-// of waves times the time of one tile: choose the width for which that is least.  Narrower
-// tiles re-read more of A per flop, so they have to win by a margin that grows as they shrink.
+// of waves times the time of one tile: choose the width for which that is least.  A tile's time
+// per K block was measured at 2,048 x 2,560 x 9,728 (clocks: 659 at width 128, 697 at 160, 780 at
+// 256): narrow tiles save far less than their width, because the 128 rows of A are fetched for
+// each of them and shared memory, not the tensor core, sets the pace.
 static int pick_bn(int M, int N, int num_sms) {
     const int tiles_m = (M + BM - 1) / BM;
     int best = 256;
     double best_cost = -1.0;
 #define SB_CONSIDER(bn) { \
         const long tiles = (long)tiles_m * ((N + bn - 1) / bn); \
-        const double cost = (double)((tiles + num_sms - 1) / num_sms) * bn * (1.0 + 0.15 * (256 - bn) / 128.0); \
+        const double cost = (double)((tiles + num_sms - 1) / num_sms) * (540.0 + 0.94 * bn); \
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; } }
     SB_PERSISTENT_WIDTHS(SB_CONSIDER)
 #undef SB_CONSIDER
     return best;
 }
+
+// Two issuing threads: at width 128 always (four accumulators fit, the epilogue still overlaps
+// the next tile), at 160 only without the SiLU*mul epilogue (one tile at a time there: with the
+// heavier epilogue exposed, gate/up lost 4 %; o and down gain 1 to 10 %).
+constexpr int row_issuers(int bn, int epi) { return bn == 128 || (bn == 160 && epi == 0) ? 2 : 1; }
 
 template <typename TC>
 int many_rows(const void* A, const void* W, void* C, int M, int N, int K, int* status, int variant, int epi,
@@ -552,8 +572,8 @@ int many_rows(const void* A, const void* W, void* C, int M, int N, int K, int* s
             return SB_ERR_ARG;
         }
 #define SB_TRY(BN_) \
-        if (bn == BN_) return epi == 1 ? launch_persistent<BN_, persistent_stages(BN_), TC, 1>(ma, mb, C, M, N, K, status, stream) \
-                                       : launch_persistent<BN_, persistent_stages(BN_), TC, 0>(ma, mb, C, M, N, K, status, stream);
+        if (bn == BN_) return epi == 1 ? launch_persistent<BN_, persistent_stages(BN_), TC, 1, row_issuers(BN_, 1)>(ma, mb, C, M, N, K, status, stream) \
+                                       : launch_persistent<BN_, persistent_stages(BN_), TC, 0, row_issuers(BN_, 0)>(ma, mb, C, M, N, K, status, stream);
         SB_PERSISTENT_WIDTHS(SB_TRY)
 #undef SB_TRY
         sb_set_error("gemm_tcgen05: no persistent kernel of width %d", bn);

@@ -116,13 +116,22 @@ __device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
 // to row m of C (columns b0 ..).  Called by whole warps: the loads are warp-wide.
 //   EPI = 0: C[m, n] = acc
 //   EPI = 1: columns interleave gate and up; C[m, f] = up * silu(gate), C has N/2 columns.
-template <int BN, typename TC, int EPI>
+//   ADD > 0: a second accumulator ADD columns further on is added to the first.
+template <int BN, typename TC, int EPI, int ADD = 0>
 __device__ __forceinline__ void drain_tile(uint32_t taddr, TC* __restrict__ C, int M, int N, int m, int b0) {
 #pragma unroll 2
     for (int c0 = 0; c0 < BN; c0 += 16) {
         uint32_t r[16];
         tmem_ld16(taddr + c0, r);
-        tmem_ld_wait();
+        if constexpr (ADD > 0) {
+            uint32_t r2[16];
+            tmem_ld16(taddr + ADD + c0, r2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 16; ++q) r[q] = __float_as_uint(__uint_as_float(r[q]) + __uint_as_float(r2[q]));
+        } else {
+            tmem_ld_wait();
+        }
         if (m >= M) continue;
         if (EPI == 1) {
             // columns come in (gate, up) pairs: 16 accumulator columns -> 8 outputs

@@ -100,7 +100,9 @@ def test_gemm_tcgen05_one_hot_rows_and_columns(ops):
                                    (70, 128, 72), (5000, 384, 96)])
 def test_gemm_tcgen05_persistent_many_tiles(ops, M, N, K):
     """Shapes that give one block several tiles (two accumulators in turn), ragged edges,
-    and every tile width; compared with the one-tile-per-block kernel too."""
+    and every tile width; compared with the one-tile-per-block kernel too: the same bits at the
+    full tile width, where one thread adds a tile's K blocks in the same order in both kernels
+    (narrower tiles add them as two halves)."""
     a, w, want = operands(M, N, K, seed=2)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
@@ -108,7 +110,10 @@ def test_gemm_tcgen05_persistent_many_tiles(ops, M, N, K):
     close(out, want, K, False)
     other = torch.empty_like(out)
     ops.gemm_tcgen05(other, a, w, status, variant=4)
-    assert torch.equal(out, other)
+    close(other, want, K, False)
+    full = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_tcgen05(full, a, w, status, variant=256)
+    assert torch.equal(full, other)
     outb = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
     ops.gemm_tcgen05(outb, a, w, status)
     close(outb, want, K, True)
