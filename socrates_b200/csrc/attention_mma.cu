@@ -11,10 +11,10 @@
 //     see the row's pages from the window's start up to their own position, earlier
 //     portions included.
 //   * attn_decode_kernel: one block per (KV head, token, key partition) for steps in
-//     which every request brings one token.  The G query heads are 16 accumulator rows
-//     shared by the four warps; each warp takes a quarter of every key tile and the
-//     warps are merged at the end; 2 to 4 partitions are merged through the cluster's shared
-//     memory, more by the reduce kernel.
+//     which every request brings one token.  The products are transposed there: a warp's 16
+//     keys are the accumulator rows and the G query heads the 8 (or 16) columns.  Each warp
+//     takes a quarter of every key tile and the warps are merged at the end; 2 to 4 partitions
+//     are merged through the cluster's shared memory, more by the reduce kernel.
 //
 // Keys outside [lo, hi) are never read from the pool (their shared-memory rows are
 // zero-filled by cp.async and their scores are masked), so whatever a page's previous
@@ -234,6 +234,124 @@ __device__ __forceinline__ void warp_tile(RowState<D>& st, const uint32_t (&qf)[
     }
 }
 
+// ---- the decode step's tile: one token, so only the G query heads of the KV head are rows.
+// With the query rows on the 16 accumulator rows of an m16n8k16 product at least half of them
+// (three quarters at G = 4) would be padding, and the products, not memory, bounded the kernel
+// (64 clocks per product and warp measured).  Here the products are transposed: the KEYS are
+// the 16 accumulator rows and the query heads the 8 columns (NBQ = 1, G <= 8) or 16 (NBQ = 2):
+//   S^T = K Q^T      A = 16 keys x 16 dims from the key tile, B = Q^T (the query fragments)
+//   O^T += V^T P^T   A = 16 dims x 16 keys (ldmatrix.trans of the value tile), B = P^T
+// which halves the products per key at G <= 8.  A thread owns two query heads (columns
+// 2*(lane%4), +1 of each column block): maxima and sums run down the columns (over the lanes
+// with the same lane%4), and P^T becomes a B operand through movmatrix.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+// m[c], l[c]: reference maximum and this thread's share of the sum of column c = 2*nb + e;
+// o[mb][nb][4]: O^T, dims 16*mb + lane/4 (+8 for [2], [3]) by the thread's two columns.
+template <int D, int NBQ> struct ColState {
+    float m[2 * NBQ], l[2 * NBQ];
+    float o[D / 16][NBQ][4];
+    __device__ __forceinline__ void init() {
+#pragma unroll
+        for (int c = 0; c < 2 * NBQ; ++c) { m[c] = -INFINITY; l[c] = 0.f; }
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i)
+#pragma unroll
+            for (int nb = 0; nb < NBQ; ++nb) o[i][nb][0] = o[i][nb][1] = o[i][nb][2] = o[i][nb][3] = 0.f;
+    }
+};
+
+// One warp: its 16 keys (kb .. kb+15 of the tile at tile_start) against the token's query heads.
+//   qf: the query fragments as loaded for an A operand (rows 0-7 and 8-15, two 8-dim chunks).
+//   Keys outside [klo, khi) or beyond qpos are masked when `masked`.
+template <int D, int NBQ>
+__device__ __forceinline__ void warp_tile_decode(ColState<D, NBQ>& st, const uint32_t (&qf)[D / 16][4],
+                                                 const bf16* ks, const bf16* vs, int kb, int tile_start, int qpos,
+                                                 int klo, int khi, float scale_log2, bool masked) {
+    const int lane = threadIdx.x & 31;
+    const int j = lane >> 3;
+    float s[NBQ][4];
+#pragma unroll
+    for (int nb = 0; nb < NBQ; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+    // ---- S^T = K Q^T
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t a[4];
+        ldmatrix_x4(a, smem_u32(ks + tile_off<D>(kb + (j & 1) * 8 + (lane & 7), kk * 2 + (j >> 1))));
+        mma_bf16(s[0], a, qf[kk][0], qf[kk][2]);
+        if constexpr (NBQ == 2) mma_bf16(s[1], a, qf[kk][1], qf[kk][3]);
+    }
+    // ---- mask: the thread's keys are rows lane/4 and lane/4 + 8
+    if (masked) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int kpos = tile_start + kb + (lane >> 2) + 8 * h;
+            const bool keep = kpos <= qpos && kpos >= klo && kpos < khi;
+#pragma unroll
+            for (int nb = 0; nb < NBQ; ++nb) {
+                s[nb][2 * h] = keep ? s[nb][2 * h] : -INFINITY;
+                s[nb][2 * h + 1] = keep ? s[nb][2 * h + 1] : -INFINITY;
+            }
+        }
+    }
+    // ---- column maxima over the warp's 16 keys, lazy move of the reference (as in warp_tile)
+    float neg_m[2 * NBQ];
+#pragma unroll
+    for (int nb = 0; nb < NBQ; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int c = 2 * nb + e;
+            float mx = fmaxf(s[nb][e], s[nb][e + 2]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const bool grow = mx > -INFINITY && (st.m[c] == -INFINITY || (mx - st.m[c]) * scale_log2 > 8.0f);
+            if (grow) {
+                const float alpha = st.m[c] == -INFINITY ? 0.f : exp2f((st.m[c] - mx) * scale_log2);
+                st.m[c] = mx;
+                st.l[c] *= alpha;
+#pragma unroll
+                for (int i = 0; i < D / 16; ++i) {
+                    st.o[i][nb][e] *= alpha;
+                    st.o[i][nb][e + 2] *= alpha;
+                }
+            }
+            neg_m[c] = st.m[c] == -INFINITY ? 0.f : -st.m[c] * scale_log2;
+        }
+    }
+    // ---- P^T = 2^(S^T*scale - m*scale), split into two bfloat16 terms, transposed into B operands
+    uint32_t bhi[NBQ][2], blo[NBQ][2];
+#pragma unroll
+    for (int nb = 0; nb < NBQ; ++nb) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {                       // keys lane/4 (h = 0) and lane/4 + 8 (h = 1)
+            const float p0 = ex2_approx(fmaf(s[nb][2 * h], scale_log2, neg_m[2 * nb]));
+            const float p1 = ex2_approx(fmaf(s[nb][2 * h + 1], scale_log2, neg_m[2 * nb + 1]));
+            st.l[2 * nb] += p0;
+            st.l[2 * nb + 1] += p1;
+            const uint32_t hi = pack_bf16(p0, p1);
+            const uint32_t lo = pack_bf16(p0 - __uint_as_float(hi << 16), p1 - __uint_as_float(hi & 0xffff0000u));
+            bhi[nb][h] = movmatrix_trans(hi);
+            blo[nb][h] = movmatrix_trans(lo);
+        }
+    }
+    // ---- O^T += V^T P^T
+#pragma unroll
+    for (int mb = 0; mb < D / 16; ++mb) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, smem_u32(vs + tile_off<D>(kb + (j >> 1) * 8 + (lane & 7), mb * 2 + (j & 1))));
+#pragma unroll
+        for (int nb = 0; nb < NBQ; ++nb) {
+            mma_bf16(st.o[mb][nb], a, bhi[nb][0], bhi[nb][1]);
+            mma_bf16(st.o[mb][nb], a, blo[nb][0], blo[nb][1]);
+        }
+    }
+}
+
 // ----------------------------------------------------------------------------- prefill
 // grid (max_tiles, Hkv).  seq_starts [R+1], seq_rows [R], seq_first_pos [R].
 template <int D>
@@ -352,7 +470,7 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf
 // CLUSTER: the NP blocks of a (token, KV head) are one thread-block cluster and merge their
 // partial results through distributed shared memory: no scratch in global memory, no reduce
 // kernel.  Every block of the cluster reaches both cluster barriers (an empty partition too).
-template <int D, int NW, int S, bool CLUSTER = false>
+template <int D, int NW, int S, bool CLUSTER = false, int NBQ = 1>
 __global__ void __launch_bounds__(32 * NW)
 attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                    const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
@@ -437,9 +555,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         }
     }
 
-    const int qpos[2] = {pos, pos};
-    const int qlo[2] = {lo, lo};
-    RowState<D> st;
+    ColState<D, NBQ> st;
     st.init();
     uint32_t qf[D / 16][4];
     for (int i = 0; i < n_tiles; ++i) {
@@ -459,42 +575,53 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         const int buf = i % S;
         const int ts = (tile_begin + i) * KTD;
         const bool masked = ts < k_begin || ts + KTD > k_end;       // only the partition's edge tiles
-        warp_tile<D, 16>(st, qf, kbuf + buf * KTD * D, vbuf + buf * KTD * D, warp * 16, ts, qpos, qlo, k_begin, k_end,
-                         scale_log2, masked);
+        warp_tile_decode<D, NBQ>(st, qf, kbuf + buf * KTD * D, vbuf + buf * KTD * D, warp * 16, ts, pos, k_begin,
+                                 k_end, scale_log2, masked);
     }
     cp_async_wait<0>();
     __syncthreads();
-    // ---- merge the warps: each writes its rows' (m, l, O) to shared memory
+    // ---- merge the warps: each writes its query heads' (m, l, O) to shared memory
     float* wo = reinterpret_cast<float*>(kbuf);             // [NW][16][D] floats: fits in the K and V buffers
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        float l = st.l[i];
-        l += __shfl_xor_sync(0xffffffffu, l, 1);
-        l += __shfl_xor_sync(0xffffffffu, l, 2);
-        const int row = (lane >> 2) + i * 8;
-        if ((lane & 3) == 0) { w_m[warp][row] = st.m[i]; w_l[warp][row] = l; }
+    for (int nb = 0; nb < NBQ; ++nb) {
 #pragma unroll
-        for (int nb = 0; nb < D / 8; ++nb) {
-            float* dst = wo + ((size_t)(warp * 16 + row)) * D + nb * 8 + 2 * (lane & 3);
-            dst[0] = st.o[nb][2 * i];
-            dst[1] = st.o[nb][2 * i + 1];
+        for (int e = 0; e < 2; ++e) {
+            const int c = 2 * nb + e;
+            float l = st.l[c];
+            l += __shfl_xor_sync(0xffffffffu, l, 4);
+            l += __shfl_xor_sync(0xffffffffu, l, 8);
+            l += __shfl_xor_sync(0xffffffffu, l, 16);
+            const int row = 8 * nb + 2 * (lane & 3) + e;    // the query head of this column
+            if (lane < 4) { w_m[warp][row] = st.m[c]; w_l[warp][row] = l; }
+#pragma unroll
+            for (int mb = 0; mb < D / 16; ++mb) {
+                float* dst = wo + ((size_t)(warp * 16 + row)) * D + mb * 16 + (lane >> 2);
+                dst[0] = st.o[mb][nb][e];
+                dst[8] = st.o[mb][nb][e + 2];
+            }
         }
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < G * D; idx += NTHR) {
         const int row = idx / D, d = idx - row * D;
+        // every warp's (max, sum, value) first, so that the loads are in flight together; a warp
+        // without a visible key (sum 0) has weight 0 whatever its other numbers are
+        float wm[NW], wl[NW], wv[NW];
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            wm[w] = w_m[w][row];
+            wl[w] = w_l[w][row];
+            wv[w] = wo[((size_t)(w * 16 + row)) * D + d];
+        }
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < NW; ++w)
-            if (w_l[w][row] > 0.f) M = fmaxf(M, w_m[w][row]);
+        for (int w = 0; w < NW; ++w) M = wl[w] > 0.f ? fmaxf(M, wm[w]) : M;
         float L = 0.f, o = 0.f;
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
-            if (w_l[w][row] > 0.f) {
-                const float f = exp2f((w_m[w][row] - M) * scale_log2);
-                L += f * w_l[w][row];
-                o += f * wo[((size_t)(w * 16 + row)) * D + d];
-            }
+            const float f = wl[w] > 0.f ? ex2_approx((wm[w] - M) * scale_log2) : 0.f;
+            L += f * wl[w];
+            o += wl[w] > 0.f ? f * wv[w] : 0.f;
         }
         const int h = h0 + row;
         if (NP == 1) {
@@ -594,7 +721,7 @@ inline bool cluster_merge_enabled() {
     return on;
 }
 
-template <int D, int NW, int S>
+template <int D, int NW, int S, int NBQ>
 int launch_decode_v(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool, const void* v_pool,
                     const int* block_table, int table_width, const int* token_rows, const int* positions, int N,
                     int Hq, int Hkv, int BS, int window, float scale, int NP, cudaStream_t stream) {
@@ -602,22 +729,22 @@ int launch_decode_v(void* out, float* part_o, float* part_ml, const void* q, con
     const bool cluster = NP >= 2 && sb_attention_decode_mma_kernels(NP) == 1;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, NW, S, false>,
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, NW, S, false, NBQ>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem + kMaxTableWidth * 4);
         if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(attn_decode_kernel<D, NW, S, true>,
+            e = cudaFuncSetAttribute(attn_decode_kernel<D, NW, S, true, NBQ>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, smem + kMaxTableWidth * 4);
         if (e != cudaSuccess) { sb_set_error("attention_mma: %s", cudaGetErrorString(e)); return (int)e; }
         configured = true;
     }
     dim3 grid(Hkv, N, NP);
     if (cluster) {
-        sb::launch_cluster(attn_decode_kernel<D, NW, S, true>, dim3(grid), dim3(32 * NW), smem + table_width * 4, stream,
+        sb::launch_cluster(attn_decode_kernel<D, NW, S, true, NBQ>, dim3(grid), dim3(32 * NW), smem + table_width * 4, stream,
             dim3(1, 1, NP), (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
             block_table, table_width, token_rows, positions, Hq, Hkv, BS, window, scale * LOG2E, NP);
         return 0;
     }
-    sb::launch(attn_decode_kernel<D, NW, S, false>, dim3(grid), dim3(32 * NW), smem + table_width * 4, stream, 
+    sb::launch(attn_decode_kernel<D, NW, S, false, NBQ>, dim3(grid), dim3(32 * NW), smem + table_width * 4, stream, 
         (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
         table_width, token_rows, positions, Hq, Hkv, BS, window, scale * LOG2E, NP);
     if (NP > 1) {
@@ -638,9 +765,12 @@ template <int D>
 int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool, const void* v_pool,
                   const int* block_table, int table_width, const int* token_rows, const int* positions, int N,
                   int Hq, int Hkv, int BS, int window, float scale, int NP, cudaStream_t stream, int variant = 0) {
-#define SB_DEC(NW, S) launch_decode_v<D, NW, S>(out, part_o, part_ml, q, k_pool, v_pool, block_table, table_width, \
-                                                token_rows, positions, N, Hq, Hkv, BS, window, scale, NP, stream)
-    return variant == 1 ? SB_DEC(4, 2) : SB_DEC(4, 3);
+#define SB_DEC(NW, S, NBQ) launch_decode_v<D, NW, S, NBQ>(out, part_o, part_ml, q, k_pool, v_pool, block_table, \
+                                                          table_width, token_rows, positions, N, Hq, Hkv, BS, window, \
+                                                          scale, NP, stream)
+    // query heads of a KV head: one block of 8 columns, or two
+    if (Hq / Hkv <= 8) return variant == 1 ? SB_DEC(4, 2, 1) : SB_DEC(4, 3, 1);
+    return variant == 1 ? SB_DEC(4, 2, 2) : SB_DEC(4, 3, 2);
 #undef SB_DEC
 }
 
