@@ -416,6 +416,98 @@ __global__ void qk_norm_rope_kvwrite_fast_kernel(
     }
 }
 
+// The same for many tokens (prompt portions), where the kernel is bound by its instruction
+// count, not by latency: half a warp per head (lane l of the half owns VPL = D/16 consecutive
+// elements, its rotation partner is lane l ^ 8), so a warp serves two heads with the
+// instructions of one.  Every shuffle is executed by all lanes whatever their heads are (the
+// two halves may hold heads of different kinds); loads and stores are predicated instead.
+template <typename T, int VPL>
+__global__ void qk_norm_rope_kvwrite_rows_kernel(
+    const T* __restrict__ qkv, const float* __restrict__ parts, int S, size_t part_stride,
+    T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool,
+    const float* __restrict__ q_gain, const float* __restrict__ k_gain,
+    const float* __restrict__ inv_freq, int R, const int* __restrict__ positions,
+    const int* __restrict__ token_rows, const int* __restrict__ block_table, int table_width,
+    int BS, float eps, int Hq, int Hkv, int write_kv, int heads_per_block) {
+    sb::pdl_launch_dependents();     // the next kernel may begin its prologue
+    constexpr int D = 16 * VPL;
+    __shared__ float cs[D / 2], sn[D / 2];
+    const int n = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane >> 4, l = lane & 15;           // which of the warp's two heads, lane within it
+    const int n_heads = Hq + 2 * Hkv;
+    const int pos = positions[n];
+    if (R == D) {
+        for (int j = threadIdx.x; j < D / 2; j += blockDim.x) {
+            const float ang = (float)pos * inv_freq[j];
+            cs[j] = cosf(ang);
+            sn[j] = sinf(ang);
+        }
+    }
+    sb::pdl_wait();                  // everything before this kernel is complete and visible
+    __syncthreads();
+    size_t kv_slot = 0;
+    if (write_kv) {
+        const int page = block_table[(size_t)token_rows[n] * table_width + pos / BS];
+        kv_slot = ((size_t)page * Hkv * BS + (pos % BS)) * D;            // + kh * BS * D per KV head
+    }
+    const int head_end = min(n_heads, (int)(blockIdx.y + 1) * heads_per_block);
+    const int nwarps = blockDim.x >> 5;
+    for (int head0 = blockIdx.y * heads_per_block + 2 * warp; head0 < head_end; head0 += 2 * nwarps) {
+        const int head = head0 + sub;
+        const bool is_q = head < Hq;
+        const bool is_k = !is_q && head < Hq + Hkv;
+        const bool is_v = !is_q && !is_k;
+        const bool live = head < head_end && (is_q || write_kv);
+        float y[VPL];
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) y[i] = 0.f;
+        if (live) {
+            const size_t base = ((size_t)n * n_heads + head) * D + l * VPL;
+            if (parts != nullptr) {
+                for (int s = 0; s < S; ++s) {               // added in the order s = 0, 1, ...
+                    const Pack<float, VPL> p = *reinterpret_cast<const Pack<float, VPL>*>(parts + s * part_stride + base);
+#pragma unroll
+                    for (int i = 0; i < VPL; ++i) y[i] += p.v[i];
+                }
+            } else {
+                const Pack<T, VPL> p = *reinterpret_cast<const Pack<T, VPL>*>(qkv + base);
+#pragma unroll
+                for (int i = 0; i < VPL; ++i) y[i] = to_float(p.v[i]);
+            }
+        }
+        const float* gain = is_q ? q_gain : (is_k ? k_gain : nullptr);
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) ss += y[i] * y[i];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);      // over the head's 16 lanes
+        if (live && gain != nullptr) {
+            const float rinv = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) y[i] = y[i] * rinv * gain[l * VPL + i];
+        }
+        Pack<T, VPL> o;
+        const bool rotate = !is_v && R == D;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const float partner = __shfl_xor_sync(0xffffffffu, y[i], 8);
+            const float c = cs[(l & 7) * VPL + i], s = sn[(l & 7) * VPL + i];
+            const float r = l < 8 ? y[i] * c - partner * s : y[i] * c + partner * s;
+            o.v[i] = from_float<T>(rotate ? r : y[i]);
+        }
+        if (!live) continue;
+        T* dst;
+        if (is_q) {
+            dst = q_out + ((size_t)n * Hq + head) * D;
+        } else {
+            const int kh = is_k ? head - Hq : head - Hq - Hkv;
+            dst = (is_k ? k_pool : v_pool) + kv_slot + (size_t)kh * BS * D;
+        }
+        *reinterpret_cast<Pack<T, VPL>*>(dst + l * VPL) = o;
+    }
+}
+
 template <typename T>
 static void qk_launch(const void* qkv, const float* parts, int S, size_t part_stride, void* q_out, void* k_pool,
                       void* v_pool, const float* q_gain, const float* k_gain, const float* inv_freq,
@@ -438,8 +530,10 @@ static void qk_launch(const void* qkv, const float* parts, int S, size_t part_st
                    inv_freq, rotary_dim, positions, token_rows, block_table, table_width, page_size, eps, Hq, Hkv
     // (Four heads' loads in flight per warp, U = 4, were measured slower for prompt portions:
     // 35.5 against 29.0 us for 2,048 tokens of the 4B shape.)
+    // Many tokens (hpb > 4): the kernel with half a warp per head (a prompt of 2,048 tokens through the 36
+    // layers of the 4B shape: 20.5 -> 19.9 ms).
 #define SB_QK_FAST(VPL_) \
-    if (hpb > 4) sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, VPL_, false>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb); \
+    if (hpb > 4) sb::launch(qk_norm_rope_kvwrite_rows_kernel<T, 2 * VPL_>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb); \
     else sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, VPL_, true>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb);
     if (fast && D == 64) { SB_QK_FAST(2) }
     else if (fast && D == 128) { SB_QK_FAST(4) }

@@ -199,6 +199,45 @@ def test_qk_norm_rope_from_partial_sums(ops, ref, dtype, D):
     assert torch.allclose(v_pool[page, :, off].float(), v, **tol(dtype))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,D,R,partial", [(5, 3, 128, 128, False), (7, 1, 64, 64, False), (4, 2, 256, 256, False),
+                                                (6, 3, 128, 0, False), (5, 1, 128, 128, True)])
+def test_qk_norm_rope_kvwrite_many_tokens(ops, ref, dtype, Hq, Hkv, D, R, partial):
+    """So many tokens that the kernel with half a warp per head runs (prompt portions): odd head
+    counts, so that the two heads of a warp are a query and a key, a key and a value, or one
+    head and nothing; all rotating or none; from split-K partial sums too."""
+    BS, eps, n = 16, 1e-5, 1500
+    k_pool, v_pool, table = paged_case([n], BS, Hkv, D, dtype)
+    k0, v0 = k_pool.clone(), v_pool.clone()
+    N = n - 20                                               # positions 20 .. n-1 of row 0
+    token_rows = torch.zeros(N, dtype=torch.int32, device=DEV)
+    positions = torch.arange(20, n, dtype=torch.int32, device=DEV)
+    width = (Hq + 2 * Hkv) * D
+    if partial:
+        parts = rand(3, N, width, seed=5)
+        src, total = parts, parts[0] + parts[1] + parts[2]
+    else:
+        src = total = rand(N, width, dtype=dtype, seed=5)
+    qg, kg = 1 + 0.1 * rand(D, seed=6), 1 + 0.1 * rand(D, seed=7)
+    inv_freq = (1.0 / (1e4 ** (torch.arange(0, max(R, 2), 2).float() / max(R, 2)))).to(DEV)
+    q_out = torch.full((N, Hq * D), float("nan"), dtype=dtype, device=DEV)
+    ops.qk_norm_rope_kvwrite(src, q_out, k_pool, v_pool, qg, kg, inv_freq, R, positions, token_rows,
+                             table, eps, Hq, Hkv, D)
+    q, k, v = ref.qk_norm_rope_ref(total, qg, kg, inv_freq, R, positions, eps, Hq, Hkv, D)
+    assert torch.allclose(q_out.float().view(N, Hq, D), q, **tol(dtype))
+    page, off = ref.kv_slots(table, token_rows, positions, BS)
+    assert torch.allclose(k_pool[page, :, off].float(), k, **tol(dtype))
+    assert torch.allclose(v_pool[page, :, off].float(), v.to(dtype).float(), **tol(dtype))
+    mask = torch.ones(k_pool.shape[0], BS, dtype=torch.bool, device=DEV)
+    mask[page, off] = False
+    assert torch.equal(k_pool.transpose(1, 2)[mask], k0.transpose(1, 2)[mask])
+    assert torch.equal(v_pool.transpose(1, 2)[mask], v0.transpose(1, 2)[mask])
+    q2 = torch.full_like(q_out, float("nan"))
+    ops.qk_norm_rope_kvwrite(src, q2, None, None, qg, kg, inv_freq, R, positions, token_rows, table,
+                             eps, Hq, Hkv, D)
+    assert torch.equal(q2, q_out)
+
+
 def test_rotation_far_positions_float32(ops, ref):
     """Angles are float32(position) * inv_freq; at position 8191 a sloppy sine shows."""
     Hq, Hkv, D = 2, 1, 64
