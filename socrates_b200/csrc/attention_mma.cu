@@ -274,17 +274,31 @@ __device__ __forceinline__ void warp_tile_decode(ColState<D, NBQ>& st, const uin
                                                  int klo, int khi, float scale_log2, bool masked) {
     const int lane = threadIdx.x & 31;
     const int j = lane >> 3;
-    float s[NBQ][4];
+    // ---- S^T = K Q^T.  The D/16 products of a column block would be one chain through their
+    // accumulator; they go to CH accumulators in turn (four chains a quarter as long), added at the end.
+    constexpr int CH = D / 16 >= 4 ? 4 : D / 16;
+    float sp[CH][NBQ][4];
 #pragma unroll
-    for (int nb = 0; nb < NBQ; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
-    // ---- S^T = K Q^T
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+        for (int nb = 0; nb < NBQ; ++nb) sp[c][nb][0] = sp[c][nb][1] = sp[c][nb][2] = sp[c][nb][3] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
         uint32_t a[4];
         ldmatrix_x4(a, smem_u32(ks + tile_off<D>(kb + (j & 1) * 8 + (lane & 7), kk * 2 + (j >> 1))));
-        mma_bf16(s[0], a, qf[kk][0], qf[kk][2]);
-        if constexpr (NBQ == 2) mma_bf16(s[1], a, qf[kk][1], qf[kk][3]);
+        mma_bf16(sp[kk % CH][0], a, qf[kk][0], qf[kk][2]);
+        if constexpr (NBQ == 2) mma_bf16(sp[kk % CH][1], a, qf[kk][1], qf[kk][3]);
     }
+    float s[NBQ][4];
+#pragma unroll
+    for (int nb = 0; nb < NBQ; ++nb)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float v = sp[0][nb][e];
+#pragma unroll
+            for (int c = 1; c < CH; ++c) v += sp[c][nb][e];
+            s[nb][e] = v;
+        }
     // ---- mask: the thread's keys are rows lane/4 and lane/4 + 8
     if (masked) {
 #pragma unroll
