@@ -116,6 +116,38 @@ __device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const bf16* __r
     }
 }
 
+// Quarter `part` (0..3) of load_kv_tile's copies: the decode kernel issues a tile's copies in
+// four doses between the phases of the tile before it.  Sixteen cp.async per thread in one
+// burst, from every warp of the SM at the same moment after the block's barrier, queue up in
+// the load/store unit: a warp then sat 1,500 clocks of a 3,400-clock tile in that burst.
+template <int D, int KTILE, int NTHR>
+__device__ __forceinline__ void load_kv_tile_part(int part, bf16* ks, bf16* vs, const bf16* __restrict__ k_pool,
+                                                  const bf16* __restrict__ v_pool, const int* table, int table_base,
+                                                  int bs_log2, int Hkv, int kh, int tile_start, int lo, int hi) {
+    constexpr int CH = D / 8;
+    constexpr int ROWS = NTHR / CH;
+    constexpr int IT = KTILE / ROWS;                // copies of one thread per tile and pool
+    static_assert(NTHR % CH == 0 && KTILE % ROWS == 0, "threads must tile the tile");
+    const int c = threadIdx.x % CH;
+    const int r0 = threadIdx.x / CH;
+    const int bs_mask = (1 << bs_log2) - 1;
+#pragma unroll
+    for (int it = 0; it < IT; ++it) {
+        if (it * 4 / IT != part) continue;          // dose `part` holds the copies it with it*4/IT == part
+        const int key = r0 + it * ROWS;
+        const int pos = tile_start + key;
+        const bool valid = pos >= lo && pos < hi;
+        size_t src = 0;
+        if (valid) {
+            const int page = table[(pos >> bs_log2) - table_base];
+            src = ((((size_t)page * Hkv + kh) << bs_log2) + (pos & bs_mask)) * D + c * 8;
+        }
+        const int off = tile_off<D>(key, c);
+        cp_async16(smem_u32(ks + off), k_pool + src, valid ? 16 : 0);
+        cp_async16(smem_u32(vs + off), v_pool + src, valid ? 16 : 0);
+    }
+}
+
 // State of the two accumulator rows a thread owns (rows lane/4 and lane/4 + 8 of the
 // warp's 16): running maximum (raw scores), this thread's share of the running sum, and
 // the output accumulators.
@@ -268,10 +300,11 @@ template <int D, int NBQ> struct ColState {
 // One warp: its 16 keys (kb .. kb+15 of the tile at tile_start) against the token's query heads.
 //   qf: the query fragments as loaded for an A operand (rows 0-7 and 8-15, two 8-dim chunks).
 //   Keys outside [klo, khi) or beyond qpos are masked when `masked`.
-template <int D, int NBQ>
+//   between(p), p = 0..3: called between the phases (the caller issues a later tile's copies there).
+template <int D, int NBQ, typename Between>
 __device__ __forceinline__ void warp_tile_decode(ColState<D, NBQ>& st, const uint32_t (&qf)[D / 16][4],
                                                  const bf16* ks, const bf16* vs, int kb, int tile_start, int qpos,
-                                                 int klo, int khi, float scale_log2, bool masked) {
+                                                 int klo, int khi, float scale_log2, bool masked, Between between) {
     const int lane = threadIdx.x & 31;
     const int j = lane >> 3;
     // ---- S^T = K Q^T.  The D/16 products of a column block would be one chain through their
@@ -288,7 +321,9 @@ __device__ __forceinline__ void warp_tile_decode(ColState<D, NBQ>& st, const uin
         ldmatrix_x4(a, smem_u32(ks + tile_off<D>(kb + (j & 1) * 8 + (lane & 7), kk * 2 + (j >> 1))));
         mma_bf16(sp[kk % CH][0], a, qf[kk][0], qf[kk][2]);
         if constexpr (NBQ == 2) mma_bf16(sp[kk % CH][1], a, qf[kk][1], qf[kk][3]);
+        if (kk == D / 32) between(0);
     }
+    between(1);
     float s[NBQ][4];
 #pragma unroll
     for (int nb = 0; nb < NBQ; ++nb)
@@ -337,6 +372,7 @@ __device__ __forceinline__ void warp_tile_decode(ColState<D, NBQ>& st, const uin
             neg_m[c] = st.m[c] == -INFINITY ? 0.f : -st.m[c] * scale_log2;
         }
     }
+    between(2);
     // ---- P^T = 2^(S^T*scale - m*scale), split into two bfloat16 terms, transposed into B operands
     uint32_t bhi[NBQ][2], blo[NBQ][2];
 #pragma unroll
@@ -363,6 +399,7 @@ __device__ __forceinline__ void warp_tile_decode(ColState<D, NBQ>& st, const uin
             mma_bf16(st.o[mb][nb], a, bhi[nb][0], bhi[nb][1]);
             mma_bf16(st.o[mb][nb], a, blo[nb][0], blo[nb][1]);
         }
+        if (mb == D / 32) between(3);
     }
 }
 
@@ -576,10 +613,6 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         cp_async_wait<S - 2>();                             // tile i has landed (this thread's share)
         __syncthreads();                                    // ... and everybody's; slot (i-1)%S is free
         const int nxt = i + S - 1;
-        if (nxt < n_tiles)
-            load_kv_tile<D, KTD, NTHR>(kbuf + (nxt % S) * KTD * D, vbuf + (nxt % S) * KTD * D, k_pool, v_pool,
-                                       stab, pg_begin, bs_log2, Hkv, kh, (tile_begin + nxt) * KTD, k_begin, k_end);
-        cp_async_commit();
         if (i == 0) {
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk)
@@ -589,8 +622,16 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         const int buf = i % S;
         const int ts = (tile_begin + i) * KTD;
         const bool masked = ts < k_begin || ts + KTD > k_end;       // only the partition's edge tiles
+        // tile nxt's copies go out in four doses between the phases of tile i (slot (i-1)%S is free)
+        auto between = [&](int part) {
+            if (nxt < n_tiles)
+                load_kv_tile_part<D, KTD, NTHR>(part, kbuf + (nxt % S) * KTD * D, vbuf + (nxt % S) * KTD * D, k_pool,
+                                                v_pool, stab, pg_begin, bs_log2, Hkv, kh, (tile_begin + nxt) * KTD,
+                                                k_begin, k_end);
+        };
         warp_tile_decode<D, NBQ>(st, qf, kbuf + buf * KTD * D, vbuf + buf * KTD * D, warp * 16, ts, pos, k_begin,
-                                 k_end, scale_log2, masked);
+                                 k_end, scale_log2, masked, between);
+        cp_async_commit();
     }
     cp_async_wait<0>();
     __syncthreads();
