@@ -37,7 +37,9 @@ def weights_checksum(w):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference")
+    ref = sys.argv[1]
     os.environ["HF_HUB_OFFLINE"] = "1"
     sys.dont_write_bytecode = True
     sys.path.insert(0, ref)
