@@ -287,12 +287,12 @@ __global__ void qk_norm_rope_kvwrite_kernel(
 // VPL consecutive elements of T as one aligned vector.
 template <typename T, int VPL> struct alignas(sizeof(T) * VPL) Pack { T v[VPL]; };
 
-// The same for head_dim = 32 * VPL with all dims rotating (R == D) or none (R == 0):
-// lane l owns elements l*VPL .. l*VPL+VPL-1, loads and stores them as one vector, and
+// The same for the few tokens of a decode step and head_dim = 32 * VPL with all dims rotating
+// (R == D) or none (R == 0): lane l owns elements l*VPL .. l*VPL+VPL-1, loads and stores them as one vector, and
 // finds its rotation partner (dim +- D/2) in lane l ^ 16.  A block serves `heads_per_block`
 // heads of one token; its first D/2 threads compute the token's cosines and sines once
 // into shared memory, so the trigonometry is not repeated for every head.
-template <typename T, int VPL, bool EARLY>
+template <typename T, int VPL>
 __global__ void qk_norm_rope_kvwrite_fast_kernel(
     const T* __restrict__ qkv, const float* __restrict__ parts, int S, size_t part_stride,
     T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool,
@@ -317,21 +317,18 @@ __global__ void qk_norm_rope_kvwrite_fast_kernel(
     // positions, rows and the block table are older than the preceding kernel (a host copy),
     // inv_freq and the gains are weights: the trigonometry above, the page of this token's key
     // and value, and this lane's gains are all there before that kernel has finished.
-    // (EARLY: the few blocks of a decode step, where every round trip after the wait counts; with
-    // many tokens the registers this takes would cost a resident block per SM, and the rows
-    // themselves hide the latency)
+    // (in the few blocks of a decode step every round trip after the wait counts; prompt portions
+    // go through qk_norm_rope_kvwrite_rows_kernel, where the rows themselves hide the latency)
     size_t kv_slot = 0;
     float gq[VPL], gk[VPL];
-    if (EARLY) {
-        if (write_kv) {
-            const int page = block_table[(size_t)token_rows[n] * table_width + pos / BS];
-            kv_slot = ((size_t)page * Hkv * BS + (pos % BS)) * D;        // + kh * BS * D per KV head
-        }
+    if (write_kv) {
+        const int page = block_table[(size_t)token_rows[n] * table_width + pos / BS];
+        kv_slot = ((size_t)page * Hkv * BS + (pos % BS)) * D;            // + kh * BS * D per KV head
+    }
 #pragma unroll
-        for (int i = 0; i < VPL; ++i) {
-            gq[i] = q_gain != nullptr ? q_gain[lane * VPL + i] : 1.f;
-            gk[i] = k_gain != nullptr ? k_gain[lane * VPL + i] : 1.f;
-        }
+    for (int i = 0; i < VPL; ++i) {
+        gq[i] = q_gain != nullptr ? q_gain[lane * VPL + i] : 1.f;
+        gk[i] = k_gain != nullptr ? k_gain[lane * VPL + i] : 1.f;
     }
     sb::pdl_wait();                  // everything before this kernel is complete and visible
     __syncthreads();
@@ -385,7 +382,7 @@ __global__ void qk_norm_rope_kvwrite_fast_kernel(
                 const float rinv = 1.0f / sqrtf(ss / (float)D + eps);
 #pragma unroll
                 for (int i = 0; i < VPL; ++i)
-                    y[u][i] = y[u][i] * rinv * (EARLY ? (is_q ? gq[i] : gk[i]) : gain[lane * VPL + i]);
+                    y[u][i] = y[u][i] * rinv * (is_q ? gq[i] : gk[i]);
             }
             Pack<T, VPL> o;
             if (!is_v && R == D) {
@@ -405,10 +402,6 @@ __global__ void qk_norm_rope_kvwrite_fast_kernel(
             } else {
                 const int kh = is_k ? head - Hq : head - Hq - Hkv;
                 T* pool = is_k ? k_pool : v_pool;
-                if (!EARLY) {
-                    const int page = block_table[(size_t)token_rows[n] * table_width + pos / BS];
-                    kv_slot = ((size_t)page * Hkv * BS + (pos % BS)) * D;
-                }
                 dst = pool + kv_slot + (size_t)kh * BS * D;
             }
             *reinterpret_cast<Pack<T, VPL>*>(dst + lane * VPL) = o;
@@ -534,7 +527,7 @@ static void qk_launch(const void* qkv, const float* parts, int S, size_t part_st
     // layers of the 4B shape: 20.5 -> 19.9 ms).
 #define SB_QK_FAST(VPL_) \
     if (hpb > 4) sb::launch(qk_norm_rope_kvwrite_rows_kernel<T, 2 * VPL_>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb); \
-    else sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, VPL_, true>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb);
+    else sb::launch(qk_norm_rope_kvwrite_fast_kernel<T, VPL_>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, write_kv, hpb);
     if (fast && D == 64) { SB_QK_FAST(2) }
     else if (fast && D == 128) { SB_QK_FAST(4) }
     else if (fast) { SB_QK_FAST(8) }
