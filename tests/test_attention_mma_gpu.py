@@ -57,7 +57,7 @@ def test_prefill_mma_portions_with_earlier_context(ops, ref, Hq, Hkv, D, window)
 
 
 @pytest.mark.parametrize("Hq,Hkv,D,NP", [(4, 2, 16, 1), (8, 2, 32, 3), (8, 8, 64, 2), (32, 8, 128, 5),
-                                         (16, 1, 64, 7), (12, 4, 128, 4)])
+                                         (16, 1, 64, 7), (12, 4, 128, 4), (12, 1, 128, 2), (10, 2, 128, 1)])
 @pytest.mark.parametrize("window", [0, 37])
 def test_decode_mma(ops, ref, Hq, Hkv, D, NP, window):
     lens = [1, 15, 16, 17, 63, 64, 65, 130, 257, 700]
