@@ -108,7 +108,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
 // trip for the 13 or 14 parts of its narrow projections; about a hundred registers, so at most
 // 640 threads a block), 2 for many rows, where the rows themselves keep memory busy.
 template <typename T, int DEPTH>
-__global__ void __launch_bounds__(DEPTH > 8 ? 640 : 1024) add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ delta,
+__global__ void __launch_bounds__(DEPTH > 8 ? 640 : 768) add_rmsnorm_vec_kernel(float* __restrict__ residual, const float* __restrict__ delta,
                                        int S, size_t delta_stride, const float* __restrict__ gain,
                                        T* __restrict__ out, const int* __restrict__ row_index, int d,
                                        float eps, int write_residual) {
@@ -128,6 +128,38 @@ __global__ void __launch_bounds__(DEPTH > 8 ? 640 : 1024) add_rmsnorm_vec_kernel
     const size_t stride4 = delta_stride / 4;
     float4* row4 = reinterpret_cast<float4*>(row);
     float ss = 0.f;
+    if constexpr (DEPTH <= 2) {
+        // Many rows: a thread owns several columns.  The residual and the first partial sum of up
+        // to three of them are loaded before any is used, so that a row costs one round trip to
+        // memory, not one per column; the sums keep the order s = 0, 1, ...
+        constexpr int CM = 3;
+        for (int i0 = threadIdx.x; i0 < d4; i0 += CM * blockDim.x) {
+            float4 v[CM], p0[CM];
+#pragma unroll
+            for (int c = 0; c < CM; ++c) {
+                const int i = i0 + c * blockDim.x;
+                if (i < d4) {
+                    v[c] = res4[i];
+                    if (S > 0) p0[c] = __ldg(del4 + i);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < CM; ++c) {
+                const int i = i0 + c * blockDim.x;
+                if (i < d4) {
+                    float4 u = v[c];
+                    if (S > 0) { u.x += p0[c].x; u.y += p0[c].y; u.z += p0[c].z; u.w += p0[c].w; }
+                    for (int s = 1; s < S; ++s) {
+                        const float4 p = __ldg(del4 + (size_t)s * stride4 + i);
+                        u.x += p.x; u.y += p.y; u.z += p.z; u.w += p.w;
+                    }
+                    row4[i] = u;
+                    if (write_residual) res4[i] = u;
+                    ss += u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w;
+                }
+            }
+        }
+    } else
     for (int i = threadIdx.x; i < d4; i += blockDim.x) {
         float4 v = res4[i];
         // DEPTH loads in flight, added in the order s = 0, 1, ...
@@ -182,7 +214,7 @@ extern "C" int sb_add_rmsnorm(float* residual, const float* delta, int S, long l
     int threads = d >= 2048 ? 512 : 256;
     if (vec) {
         threads = ((d / 4 + 31) / 32) * 32;
-        if (threads > (M <= 64 ? 640 : 1024)) threads = M <= 64 ? 640 : 1024;
+        if (threads > (M <= 64 ? 640 : 768)) threads = M <= 64 ? 640 : 768;
         if (M > 512 && threads > 256) threads = 256;
     }
 #define SB_NORM_LAUNCH(KERNEL, ...)                                                                      \
