@@ -1,12 +1,16 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 4b|8b|32b]
 
 Default run: the layer sizes of the Qwen3-4B shape (36 layers, hidden 2560, 32 query
 heads over 8 KV heads, head_dim 128, intermediate 9728, vocabulary 151936, tied head),
 random weights, bfloat16, batch 8, 2,048-token contexts in 8,192-token rows, 16-slot
-pages.  One "step" is one decode step of the whole batch.  It prints ONE JSON line:
+pages.  One "step" is one decode step of the whole batch.  `--shape 32b` runs the same
+points on the Qwen3-32B shape at 4,096-token contexts; `--shape 8b` runs continuous
+batching through the scheduler (64 requests, Poisson arrivals) on the Qwen3-8B shape.
+`--impl reference` runs the unmodified reference engine on the same workload
+(baseline/reference_arm.py).  It prints ONE JSON line:
 
   value      decoded tokens a second, K steps timed on the device with CUDA events;
   e2e        the same through the Python entry point (Engine.step), host tokens in and out;
@@ -32,13 +36,19 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-QWEN3_4B = {
-    "architectures": ["Qwen3ForCausalLM"], "vocab_size": 151936, "hidden_size": 2560,
-    "intermediate_size": 9728, "num_hidden_layers": 36, "num_attention_heads": 32,
-    "num_key_value_heads": 8, "head_dim": 128, "rms_norm_eps": 1e-6, "rope_theta": 1e6,
-    "tie_word_embeddings": True, "max_position_embeddings": 40960,
+def _qwen3(hidden, inter, layers, heads, tied):
+    return {"architectures": ["Qwen3ForCausalLM"], "vocab_size": 151936, "hidden_size": hidden,
+            "intermediate_size": inter, "num_hidden_layers": layers, "num_attention_heads": heads,
+            "num_key_value_heads": 8, "head_dim": 128, "rms_norm_eps": 1e-6, "rope_theta": 1e6,
+            "tie_word_embeddings": tied, "max_position_embeddings": 40960}
+
+
+# The three real shapes of the benchmark: (name, config.json keys, context of the decode points)
+SHAPES = {
+    "4b": ("Qwen3-4B", _qwen3(2560, 9728, 36, 32, True), 2048),
+    "8b": ("Qwen3-8B", _qwen3(4096, 12288, 36, 32, False), 2048),
+    "32b": ("Qwen3-32B", _qwen3(5120, 25600, 64, 64, False), 4096),
 }
-FULL_LAYERS = 36
 
 
 def peaks():
@@ -123,60 +133,57 @@ def arithmetic(cfg, layers):
     return decode_bytes, prefill_flops
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=2048)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS,
-                    help="fewer layers than the configuration has (both numbers are reported)")
-    ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--skip-e2e", action="store_true")
-    ap.add_argument("--skip-prefill", action="store_true")
-    args = ap.parse_args()
-
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
-        return 0
-    if args.gpus != 1:
-        print("bench.py: this engine runs on one GPU; --gpus must be 1")
-        return 2
-    args.warmup = max(args.warmup, 3)
-
+def build_engine(args, cfg_dict, rows, num_blocks, max_new, token_budget=2048):
     import torch
 
     from socrates_b200 import Engine
     from socrates_b200.config import config_from_dict
     from socrates_b200.engine.engine import build_random_model
-    from socrates_b200.engine.runner import SamplingArgs, StepEntry
 
     torch.cuda.set_device(0)
-    dev = torch.device("cuda:0")
-    cfg_dict = dict(QWEN3_4B, num_hidden_layers=args.layers)
     config = config_from_dict(cfg_dict)
+    model = build_random_model(config, 0, torch.bfloat16, torch.device("cuda:0"))
+    return Engine(model, device="cuda:0", dtype="bfloat16", compile=True, max_batch=rows, max_len=8192,
+                  max_new_tokens=max_new, block_size=16, num_blocks=num_blocks,
+                  token_budget=max(token_budget, rows))
+
+
+def shape_config(name, cfg, layers):
+    return {"model": f"{name} shape", "layers": layers, "layers_full": cfg["num_hidden_layers"],
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+            "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+            "tied_head": cfg["tie_word_embeddings"]}
+
+
+def run_decode(args, name, cfg_full):
+    """Decode at batch 1/8/64 and one 2,048-token prefill, device-timed; the batch-8 loop again
+    through Engine.step() for the end-to-end figure."""
+    import torch
+
+    from socrates_b200.engine.runner import SamplingArgs, StepEntry
+
+    dev = torch.device("cuda:0")
+    layers = args.layers or cfg_full["num_hidden_layers"]
+    cfg_dict = dict(cfg_full, num_hidden_layers=layers)
     pk = peaks()
-    decode_bytes, prefill_flops = arithmetic(cfg_dict, args.layers)
+    decode_bytes, prefill_flops = arithmetic(cfg_dict, layers)
     V = cfg_dict["vocab_size"]
     gen = torch.Generator().manual_seed(0)
     K, W, B, ctx = args.steps, args.warmup, args.batch, args.context
     max_len, page = 8192, 16
 
-    model = build_random_model(config, 0, torch.bfloat16, dev)
     rows_needed = max(B, 1 if args.skip_points else 64)
     pages_per_row = -(-(ctx + 2 * (K + W) + rows_needed + 96) // page)
-    engine = Engine(model, device="cuda:0", dtype="bfloat16", compile=True, max_batch=rows_needed,
-                    max_len=max_len, max_new_tokens=K + W + rows_needed + 32, block_size=page,
-                    num_blocks=rows_needed * pages_per_row + 8, token_budget=max(2048, rows_needed))
+    engine = build_engine(args, cfg_dict, rows_needed, rows_needed * pages_per_row + 8,
+                          K + W + rows_needed + 32)
     cache, runner = engine.cache, engine.runner
     for g in cache.groups:                      # live KV: any finite values, the bytes are what is timed
         g.k.normal_(0, 1, generator=None)
         g.v.normal_(0, 1, generator=None)
 
-    def decode_run(batch, steps, warmup, sampler=None):
-        """`steps` decode steps of `batch` rows at `ctx` tokens; returns (ms per step, clocks)."""
+    def decode_run(batch, steps, warmup):
+        """`steps` decode steps of `batch` rows at `ctx` tokens; returns (ms per step, launches, span)."""
         for r in range(batch):
             cache.assign(r)
             assert cache.reserve(r, ctx + steps + warmup + 1)
@@ -214,14 +221,14 @@ def main():
     ms, launches, span = decode_run(B, K, W)
     clocks = sampler.summary(*span)
     value = B * 1000.0 / ms
-    need = decode_bytes(B, ctx)
-    achieved = need / (ms * 1e-3) / 1e9
+    achieved = decode_bytes(B, ctx) / (ms * 1e-3) / 1e9
 
     points = {}
     if not args.skip_points:
         for b in (1, 64):
             pms, _, _ = decode_run(b, max(8, K // 2), W)
             points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
+            points[f"decode_b{b}_hbm_frac"] = round(decode_bytes(b, ctx) / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
 
     prefill = None
     if not args.skip_prefill:
@@ -270,19 +277,17 @@ def main():
             r.cancelled = True
         engine.scheduler.sweep()
         e2e = {"value": round(made / dt, 1), "unit": "tokens/s",
-               "h2d_bytes_per_step": runner.layout.total * 4, "d2h_bytes_per_step": B * 4}
+               "h2d_bytes_per_step": runner.layout.total * 4, "d2h_bytes_per_step": (B + 1) * 4}
     sampler.stop()
 
     line = {
-        "metric": "decode tokens/s (Qwen3-4B shape, batch 8, 2048-token contexts)",
+        "metric": f"decode tokens/s ({name} shape, batch {B}, {ctx}-token contexts)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), token ids uniform over the vocabulary",
-        "config": {"model": "Qwen3-4B shape", "layers": args.layers, "layers_full": FULL_LAYERS,
-                   "hidden": 2560, "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 9728,
-                   "vocab": V, "tied_head": True, "global_batch": B, "seq_len": ctx, "max_len": max_len,
-                   "page_size": page, "parallelism": "single GPU", "cuda_graph": True,
-                   "l2": "inputs larger than L2 (weights 8 GB per step)", "peaks": pk["source"]},
+        "config": dict(shape_config(name, cfg_full, layers), global_batch=B, seq_len=ctx, max_len=max_len,
+                       page_size=page, parallelism="single GPU", cuda_graph=True,
+                       l2="inputs larger than L2 (the weights of a step)", peaks=pk["source"]),
         "clocks": clocks, "gpu_launches": launches, "impl": "ours",
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
@@ -297,8 +302,132 @@ def main():
     return 0
 
 
-REFERENCE_UNAVAILABLE = ("pip install of the reference fails offline: its build backend hatchling is not in "
-                         "/opt/wheelhouse (ModuleNotFoundError: No module named 'hatchling')")
+def run_serve(args, name, cfg_full):
+    """Continuous batching through Engine: `--requests` requests with prompt lengths uniform in
+    [128, 4096] arrive as a Poisson process of `--rate` a second (seeded), each generates
+    `--max-new` tokens; the page pool is sized from free memory.  The load has the shape of the
+    reference's own load generator (backend/server.py:443-447: seeded exponential gaps), with
+    token ids in place of its prompt texts.  A "step" here is one Engine.step()."""
+    import random
+
+    import torch
+
+    layers = args.layers or cfg_full["num_hidden_layers"]
+    cfg_dict = dict(cfg_full, num_hidden_layers=layers)
+    V = cfg_dict["vocab_size"]
+    n, max_new = args.requests, args.max_new
+    engine = build_engine(args, cfg_dict, 64, None, max_new)
+    engine.warmup()
+    rng = random.Random(0)
+    gen = torch.Generator().manual_seed(0)
+    lengths = [rng.randint(128, 4096) for _ in range(n)]
+    arrivals, t = [], 0.0
+    for _ in range(n):
+        t += rng.expovariate(args.rate)
+        arrivals.append(t)
+    prompts = [torch.randint(1, V, (L,), generator=gen).tolist() for L in lengths]
+
+    sampler = ClockSampler()
+    sampler.start()
+    time.sleep(0.3)
+    sch, runner = engine.scheduler, engine.runner
+    reqs, step_tokens = [], []
+    before = runner.kernel_launches
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    i = 0
+    while i < n or sch.has_work():
+        now = time.perf_counter() - t0
+        while i < n and arrivals[i] <= now:
+            r = engine.submit(prompts[i], max_new_tokens=max_new)
+            r.submitted = t0 + arrivals[i]          # the moment it was due, not the moment the loop saw it
+            reqs.append(r)
+            i += 1
+        done = sch.prompt_tokens + sch.output_tokens
+        if engine.step():
+            step_tokens.append(sch.prompt_tokens + sch.output_tokens - done)
+        elif i < n:
+            time.sleep(max(0.0, min(0.002, arrivals[i] - (time.perf_counter() - t0))))
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    sampler.stop()
+    wall = t1 - t0
+    out_tokens = sum(len(r.output) for r in reqs)
+    assert all(r.done for r in reqs) and out_tokens == n * max_new
+
+    def pct(xs, q):
+        xs = sorted(xs)
+        return xs[min(len(xs) - 1, int(q * len(xs)))]
+
+    ttft = [r.first_token - r.submitted for r in reqs]
+    itl = [(r.finished - r.first_token) / max(1, len(r.output) - 1) for r in reqs]
+    steps = len(step_tokens)
+    pk = peaks()
+    line = {
+        "metric": f"continuous batching output tokens/s ({name} shape, {n} requests, Poisson {args.rate}/s)",
+        "value": round(out_tokens / wall, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": 0,
+        "ms_per_step": round(wall * 1e3 / steps, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02), token ids uniform over the vocabulary, seeded arrivals",
+        "config": dict(shape_config(name, cfg_full, layers), global_batch=64, seq_len="128..4096 prompt",
+                       max_len=8192, page_size=16, parallelism="single GPU", cuda_graph=True,
+                       requests=n, rate_per_s=args.rate, max_new=max_new,
+                       pool_pages=engine.cache.groups[0].allocator.num_pages, peaks=pk["source"]),
+        "clocks": sampler.summary(t0, t1), "gpu_launches": runner.kernel_launches - before, "impl": "ours",
+        "e2e": {"value": round(out_tokens / wall, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": runner.layout.total * 4, "d2h_bytes_per_step": 65 * 4},
+        "serve": {"wall_s": round(wall, 2), "prompt_tokens": sum(lengths), "output_tokens": out_tokens,
+                  "total_tokens_per_s": round((sum(lengths) + out_tokens) / wall, 1),
+                  "mean_tokens_per_step": round(sum(step_tokens) / steps, 1),
+                  "preemptions": sch.preemptions, "ahead_launched": engine.ahead_launched,
+                  "ahead_discarded": engine.ahead_discarded,
+                  "ttft_s": {"p50": round(pct(ttft, 0.5), 4), "p99": round(pct(ttft, 0.99), 4)},
+                  "itl_ms": {"p50": round(pct(itl, 0.5) * 1e3, 3), "p99": round(pct(itl, 0.99) * 1e3, 3)}},
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--shape", default="4b", choices=sorted(SHAPES),
+                    help="4b (the headline), 32b: decode and prefill points; 8b: continuous batching")
+    ap.add_argument("--workload", default=None, choices=("decode", "serve"),
+                    help="default: serve for 8b, decode for the others")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None,
+                    help="fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--requests", type=int, default=64)
+    ap.add_argument("--rate", type=float, default=4.0)
+    ap.add_argument("--max-new", type=int, default=512)
+    ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-prefill", action="store_true")
+    args = ap.parse_args()
+
+    if args.gpus != 1:
+        print("bench.py: this engine runs on one GPU; --gpus must be 1")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    name, cfg_full, ctx = SHAPES[args.shape]
+    args.context = args.context or ctx
+    workload = args.workload or ("serve" if args.shape == "8b" else "decode")
+
+    if args.impl == "reference":
+        sys.path.insert(0, str(ROOT / "baseline"))
+        import reference_arm
+        layers = args.layers or cfg_full["num_hidden_layers"]
+        return reference_arm.run(args, dict(cfg_full, num_hidden_layers=layers), name,
+                                 cfg_full["num_hidden_layers"], ClockSampler, peaks, arithmetic)
+    if workload == "serve":
+        return run_serve(args, name, cfg_full)
+    return run_decode(args, name, cfg_full)
+
 
 if __name__ == "__main__":
     sys.exit(main())

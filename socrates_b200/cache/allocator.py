@@ -1,14 +1,22 @@
-"""Host-side free list of cache pages.
+"""Host-side bookkeeping of which cache pages are out and which can be handed out.
 
-Same contract as the reference's BlockAllocator (model/paging.py:22-65): pages are
-numbered 1..num_pages, page 0 is the null page and is never handed out, freed pages
-are reused last-in first-out, `alloc` fails without side effects, and `free`
-validates every page before it changes anything.
+The contract is the one the reference's block allocator keeps (model/paging.py:22-65):
+usable pages are numbered 1..num_pages, page 0 stands for "no page" and never leaves,
+the page given back last is handed out first, a request for more pages than are free
+changes nothing, and a `free` that names a bad page changes nothing either.
+
+The form is this engine's own: a fixed stack of page numbers with a fill mark, and
+one state byte per page.  The byte answers "is this page out?" in O(1), which is
+what `free`, `holds` and `check` are built on; a cache group with hundreds of
+thousands of pages allocates nothing after construction.
 """
 
 from __future__ import annotations
 
+from array import array
 from typing import Iterable, List
+
+_IN, _OUT, _LEAVING = 0, 1, 2        # page state: in the stack, held by a row, named by the free() in progress
 
 
 class OutOfPages(Exception):
@@ -27,45 +35,69 @@ class PageAllocator:
         if num_pages < 1:
             raise ValueError("a pool needs at least one usable page")
         self.num_pages = num_pages
-        self._free: List[int] = list(range(num_pages, 0, -1))   # popped from the end: 1, 2, 3, ...
-        self._used: set[int] = set()
+        # _stack[:_fill] are the pages that are in; the top of the stack leaves first, and
+        # the stack starts with page 1 on top
+        self._stack = array("i", range(num_pages, 0, -1))
+        self._fill = num_pages
+        self._state = bytearray(num_pages + 1)
+        self._state[self.NULL] = _LEAVING                 # never in, never out: no transition accepts it
 
     @property
     def n_free(self) -> int:
-        return len(self._free)
+        return self._fill
 
     @property
     def n_used(self) -> int:
-        return len(self._used)
+        return self.num_pages - self._fill
+
+    def holds(self, page: int) -> bool:
+        """Whether `page` is out (held by somebody) right now."""
+        return 0 < page <= self.num_pages and self._state[page] == _OUT
 
     def alloc(self, n: int) -> List[int]:
         if n < 0:
-            raise ValueError(f"cannot allocate {n} pages")
-        if n > len(self._free):
-            raise OutOfPages(f"asked for {n} pages, {len(self._free)} free")
-        out = [self._free.pop() for _ in range(n)]
-        self._used.update(out)
-        return out
+            raise ValueError(f"a request for {n} pages makes no sense")
+        if n > self._fill:
+            raise OutOfPages(f"{n} pages wanted but only {self._fill} of {self.num_pages} are in")
+        top = self._fill
+        taken = [self._stack[top - 1 - i] for i in range(n)]
+        self._fill = top - n
+        for p in taken:
+            self._state[p] = _OUT
+        return taken
 
     def free(self, pages: Iterable[int]) -> None:
-        pages = list(pages)
-        seen = set()
-        for p in pages:
-            if p == self.NULL:
-                raise ValueError("page 0 is the null page and is never allocated")
-            if p not in self._used or p in seen:
-                raise ValueError(f"page {p} freed twice, or never allocated")
-            seen.add(p)
+        pages = [int(p) for p in pages]
+        # first pass marks, so a page named twice in one call is seen; any fault undoes the marks
+        for i, p in enumerate(pages):
+            if not 0 <= p <= self.num_pages or self._state[p] != _OUT:
+                for q in pages[:i]:
+                    self._state[q] = _OUT
+                if p == self.NULL:
+                    raise ValueError("the null page (0) is nobody's to give back")
+                raise ValueError(f"page {p} is not out: given back already, named twice, or not of this pool")
+            self._state[p] = _LEAVING
+        # pushed back to front, so the pages come out again in the order they were named
         for p in reversed(pages):
-            self._used.remove(p)
-            self._free.append(p)
+            self._stack[self._fill] = p
+            self._fill += 1
+            self._state[p] = _IN
 
     def check(self) -> None:
-        """Every page is either free or used, exactly once."""
-        free = set(self._free)
-        if len(free) != len(self._free):
-            raise AssertionError("a page is on the free list twice")
-        if free & self._used:
-            raise AssertionError(f"pages both free and used: {sorted(free & self._used)}")
-        if free | self._used != set(range(1, self.num_pages + 1)):
-            raise AssertionError("a page was lost")
+        """Every usable page is in the stack exactly once or out, never both, none missing."""
+        seen = bytearray(self.num_pages + 1)
+        for i in range(self._fill):
+            p = self._stack[i]
+            if not 0 < p <= self.num_pages:
+                raise AssertionError(f"the stack holds {p}, which is no page of this pool")
+            if seen[p]:
+                raise AssertionError(f"page {p} is in the stack twice")
+            if self._state[p] != _IN:
+                raise AssertionError(f"page {p} is in the stack and marked as out")
+            seen[p] = 1
+        out = sum(1 for p in range(1, self.num_pages + 1) if self._state[p] == _OUT)
+        stale = [p for p in range(1, self.num_pages + 1) if self._state[p] == _LEAVING]
+        if stale:
+            raise AssertionError(f"pages left half-freed: {stale}")
+        if out + self._fill != self.num_pages:
+            raise AssertionError("a page was lost: neither in the stack nor out")

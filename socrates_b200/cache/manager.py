@@ -117,6 +117,14 @@ class CacheManager:
         self._staging: List[Tuple[torch.Tensor, Optional[torch.cuda.Event]]] = []
         self._staging_next = 0
 
+    @staticmethod
+    def bytes_per_page(needs: Sequence[Optional[CacheNeeds]], page_size: int, dtype: torch.dtype) -> int:
+        """Device bytes that one more page per group costs (keys and values of every layer run
+        of every group), for sizing the pool from a memory budget."""
+        item = torch.empty((), dtype=dtype).element_size()
+        return sum(2 * n.paged.num_kv_heads * page_size * n.paged.head_dim * item
+                   for n in needs if n is not None and n.paged is not None)
+
     # ------------------------------------------------------------------ views for mixers
     def pools(self, entry: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """K and V pools `[pages+1, Hkv, BS, D]` of one order entry."""
@@ -308,7 +316,7 @@ class CacheManager:
                         raise AssertionError(f"table of row {row} block {b} disagrees with ownership")
             if len(owned) != len(set(owned)):
                 raise AssertionError("a page is held by two rows")
-            if set(owned) != g.allocator._used:
+            if len(owned) != g.allocator.n_used or not all(g.allocator.holds(p) for p in owned):
                 raise AssertionError("pages owned by rows differ from pages marked used")
             if PageAllocator.NULL in owned:
                 raise AssertionError("the null page is owned")

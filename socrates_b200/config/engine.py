@@ -18,7 +18,8 @@ class EngineConfig:
     max_len: int = 8192               # tokens one row may hold
     max_new_tokens: int = 1024
     block_size: int = 16              # slots per page
-    num_blocks: Optional[int] = None  # pages per cache group; None = max_batch * ceil(max_len / block_size)
+    num_blocks: Optional[int] = None  # pages per cache group; None = from free memory (see pages_from_memory)
+    kv_memory_fraction: float = 0.9   # share of the memory left after the weights that pages may take
     token_budget: int = 2048          # most tokens one step runs
     max_queue: Optional[int] = None   # None = 16 * max_batch
     dtype: str = "bfloat16"           # "bfloat16" or "float32"
@@ -37,6 +38,8 @@ class EngineConfig:
             raise ValueError(f"dtype must be 'bfloat16' or 'float32', not {self.dtype!r}")
         if self.num_blocks is not None and self.num_blocks < 1:
             raise ValueError("num_blocks must be at least 1")
+        if not 0.0 < self.kv_memory_fraction <= 1.0:
+            raise ValueError("kv_memory_fraction must be in (0, 1]")
 
     @property
     def blocks_per_row(self) -> int:
@@ -48,4 +51,16 @@ class EngineConfig:
 
     @property
     def pool_blocks(self) -> int:
+        """Pages per group when nothing limits them: every row at its full length, which is
+        the reference's rule (model/inference_paged.py:83-84)."""
         return self.num_blocks if self.num_blocks is not None else self.max_batch * self.blocks_per_row
+
+    def pages_from_memory(self, free_bytes: int, bytes_per_page: int) -> int:
+        """Pages per group for `num_blocks=None`: what `kv_memory_fraction` of the memory that
+        is free once the weights are loaded pays for, never more than every row at full length
+        would use, never fewer than one row needs.  Pages are taken lazily and the scheduler
+        preempts when they run out, so a pool smaller than rows x max_len is safe."""
+        if self.num_blocks is not None:
+            return self.num_blocks
+        afford = int(free_bytes * self.kv_memory_fraction) // max(1, bytes_per_page)
+        return max(self.blocks_per_row, min(self.max_batch * self.blocks_per_row, afford))

@@ -751,7 +751,8 @@ int launch_prefill(void* out, const void* q, const void* k_pool, const void* v_p
                    int table_width, const int* seq_starts, const int* seq_rows, const int* seq_first_pos, int R,
                    int N, int Hq, int Hkv, int BS, int window, float scale, cudaStream_t stream) {
     auto kernel = attn_prefill_kernel<D>;
-    static bool configured = false;
+    static sb::OncePerDevice once_per_device;
+    bool& configured = once_per_device.flag();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              prefill_smem<D>() + kMaxTableWidth * 4);
@@ -782,7 +783,8 @@ int launch_decode_v(void* out, float* part_o, float* part_ml, const void* q, con
                     int Hq, int Hkv, int BS, int window, float scale, int NP, cudaStream_t stream) {
     constexpr int smem = decode_smem<D, NW, S>();
     const bool cluster = NP >= 2 && sb_attention_decode_mma_kernels(NP) == 1;
-    static bool configured = false;
+    static sb::OncePerDevice once_per_device;
+    bool& configured = once_per_device.flag();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, NW, S, false, NBQ>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem + kMaxTableWidth * 4);

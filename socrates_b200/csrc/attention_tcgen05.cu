@@ -565,7 +565,8 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, void* out, const void* 
            int table_width, const int* seq_starts, const int* seq_rows, const int* seq_first_pos, int R, int N,
            int Hq, int Hkv, int BS, int window, float scale, int* status, cudaStream_t stream) {
     auto kernel = attn_prefill_tcgen05_kernel<D>;
-    static bool configured = false;
+    static sb::OncePerDevice once_per_device;
+    bool& configured = once_per_device.flag();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              smem_bytes<D>() + 4096 * 4);

@@ -53,6 +53,18 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 
 bool pdl_enabled();    // host: false when SOCRATES_PDL=0
 
+// Host: one flag per device, for set-up that the runtime keeps per device (a kernel's opt-in to
+// large dynamic shared memory above all).  `flag()` is the current device's flag.  What such
+// set-up caches beside the flag (SM counts) assumes that the devices of a process are alike.
+struct OncePerDevice {
+    bool done[64] = {};
+    bool& flag() {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        return done[dev & 63];
+    }
+};
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                           Args&&... args) {

@@ -373,7 +373,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, 
            int* status, cudaStream_t stream) {
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, SWAP, TC, EPI>;
     constexpr int smem = STAGES * stage_bytes<BN>() + 1024;
-    static bool configured = false;
+    static sb::OncePerDevice once_per_device;
+    bool& configured = once_per_device.flag();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) { sb_set_error("gemm_tcgen05: %s", cudaGetErrorString(e)); return (int)e; }

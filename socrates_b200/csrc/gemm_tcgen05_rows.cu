@@ -448,7 +448,8 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int
                       cudaStream_t stream) {
     auto kernel = gemm_tcgen05_persistent_kernel<BN, STAGES, TC, EPI, ISSUERS>;
     constexpr int smem = STAGES * stage_bytes<BN>() + 1024;
-    static bool configured = false;
+    static sb::OncePerDevice once_per_device;
+    bool& configured = once_per_device.flag();
     static int num_sms = 0;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -470,7 +471,8 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, in
                 cudaStream_t stream) {
     auto kernel = gemm_tcgen05_pair_kernel<BN, STAGES, TC, EPI>;
     constexpr int smem = STAGES * pair_stage_bytes<BN>() + 1024;
-    static bool configured = false;
+    static sb::OncePerDevice once_per_device;
+    bool& configured = once_per_device.flag();
     static int max_pairs = 0;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

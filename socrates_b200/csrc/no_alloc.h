@@ -23,7 +23,9 @@
  *
  * First call.  The first call on each device looks up the array's device address
  * (cudaGetSymbolAddress, with that device current) and configures the kernel; make
- * that first call before any stream capture begins on that device.
+ * that first call before any stream capture begins on that device.  The address is kept
+ * in a plain per-device table without a lock: two host threads that both make a device's
+ * first call look the same address up twice and store the same value, which is harmless.
  *
  * Sharing.  All calls on a device use the same array, and it keeps whatever the last
  * call left in it.  Nothing in it has to start at zero: every partition slot that is

@@ -40,12 +40,16 @@ class Buffers:
 
     `take(name, rows, shape, dtype)` returns the first `rows` rows of a buffer that is
     allocated once for `max_rows` rows, so a CUDA graph that recorded its address stays
-    valid.  `take_flat` serves buffers whose size does not scale with the row count; if
-    one has to grow, the old storage is kept alive for the graphs that recorded it.
+    valid.  `take_wanted` does the same for buffers that hold one row per wanted logit
+    (at most `max_wanted` rows: a generation step wants one row per request, far fewer
+    than it has tokens, and a row of logits is as wide as the vocabulary).  `take_flat`
+    serves buffers whose size does not scale with the row count; if one has to grow, the
+    old storage is kept alive for the graphs that recorded it.
     """
 
-    def __init__(self, max_rows: int, device):
+    def __init__(self, max_rows: int, device, max_wanted: Optional[int] = None):
         self.max_rows = max_rows
+        self.max_wanted = max_rows if max_wanted is None else max_wanted
         self.device = device
         self._by_name: Dict[Tuple[str, tuple, torch.dtype], torch.Tensor] = {}
         self._flat: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
@@ -58,6 +62,16 @@ class Buffers:
         buf = self._by_name.get(key)
         if buf is None:
             buf = torch.empty((self.max_rows, *shape), dtype=dtype, device=self.device)
+            self._by_name[key] = buf
+        return buf[:rows]
+
+    def take_wanted(self, name: str, rows: int, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        if rows > self.max_wanted:
+            raise ValueError(f"{rows} wanted rows exceed the step limit of {self.max_wanted}")
+        key = ("wanted:" + name, tuple(shape), dtype)
+        buf = self._by_name.get(key)
+        if buf is None:
+            buf = torch.empty((self.max_wanted, *shape), dtype=dtype, device=self.device)
             self._by_name[key] = buf
         return buf[:rows]
 

@@ -27,6 +27,7 @@ from ..sampling import SamplingParams
 from ..weights import load_weights, random_tensors_on_device
 from .model import Model
 from .runner import ModelRunner, SamplingArgs, StepEntry
+from .tokenizer import encode_prompt
 from .scheduler import PlannedEntry, QueueFull, Request, Scheduler, StepPlan, TooLong
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
@@ -61,7 +62,7 @@ class Engine:
                  compile: bool = True, max_batch: int = 64, max_len: int = 8192,
                  max_new_tokens: int = 1024, block_size: int = 16, num_blocks: Optional[int] = None,
                  token_budget: int = 2048, max_queue: Optional[int] = None, warmup: bool = False,
-                 run_ahead: bool = True):
+                 run_ahead: bool = True, kv_memory_fraction: float = 0.9):
         if not torch.cuda.is_available():
             raise RuntimeError("socrates_b200.Engine needs a CUDA device; there is no CPU path")
         require_kernels()                      # fail at start-up, not on the first step
@@ -69,7 +70,7 @@ class Engine:
                                    block_size=block_size, num_blocks=num_blocks,
                                    token_budget=max(token_budget, max_batch), max_queue=max_queue,
                                    dtype="float32" if resolve_dtype(dtype) == torch.float32 else "bfloat16",
-                                   compile=compile)
+                                   compile=compile, kv_memory_fraction=kv_memory_fraction)
         self.config.validate()
         self.device = torch.device(device)
         self.dtype = resolve_dtype(dtype)
@@ -81,12 +82,22 @@ class Engine:
         self.tok = tok
         self.max_batch, self.max_len, self.max_new_tokens = max_batch, max_len, max_new_tokens
 
-        self.cache = CacheManager(self.model.cache_needs(), max_rows=max_batch, max_len=max_len,
-                                  page_size=block_size, num_pages=self.config.pool_blocks,
+        # Pages: as many as num_blocks says, else what the memory left after the weights pays
+        # for (the step's scratch is small beside it and comes out of the fraction kept back).
+        needs = self.model.cache_needs()
+        free_bytes, _ = torch.cuda.mem_get_info(self.device)
+        self.num_blocks = self.config.pages_from_memory(
+            free_bytes, CacheManager.bytes_per_page(needs, block_size, self.dtype))
+        if num_blocks is None and self.num_blocks < self.config.pool_blocks:
+            print(f"page pool: {self.num_blocks} pages of {block_size} slots per cache group "
+                  f"({self.config.pool_blocks} would hold every row at full length); "
+                  f"requests are preempted when pages run out", flush=True)
+        self.cache = CacheManager(needs, max_rows=max_batch, max_len=max_len,
+                                  page_size=block_size, num_pages=self.num_blocks,
                                   dtype=self.dtype, device=self.device)
         self.runner = ModelRunner(self.model, self.cache, self.dtype, self.device,
                                   max_tokens=self.config.token_budget, max_seqs=max_batch,
-                                  use_graphs=compile)
+                                  use_graphs=compile, max_wanted=max_batch)
         stop = set(getattr(self.model_config, "eos_token_ids", ()) or ())
         if tok is not None:
             stop |= set(getattr(tok, "all_special_ids", ()) or ())
@@ -122,12 +133,7 @@ class Engine:
             if self.tok is None:
                 raise ValueError("a text prompt needs a tokenizer (Engine(..., tok=...)); pass token ids instead")
             text = prompt
-            templ = self.tok.apply_chat_template(
-                [{"role": "user", "content": prompt}], tokenize=False, add_generation_prompt=True,
-                enable_thinking=False)
-            enc = self.tok(templ)
-            ids = enc.input_ids[0] if isinstance(enc.input_ids[0], (list, tuple)) else list(enc.input_ids)
-            ids = [int(i) for i in ids]
+            ids = encode_prompt(self.tok, prompt)
         else:
             ids = [int(i) for i in prompt]
         vocab = self.model.plan.vocab_size
@@ -153,6 +159,11 @@ class Engine:
         every live request decodes in `plan`, none can end by length, nobody waits to be
         admitted, and each row has (or gets) the page for one more token.  None otherwise."""
         sch = self.scheduler
+        if self.cache.states:
+            # A step launched early may be dropped and run again.  That is harmless for paged
+            # keys (the dropped step wrote past the rows' lengths) but not for a mixer's
+            # per-request state, which the dropped step has already advanced by one token.
+            return None
         if sch.pending or plan.preempted or len(plan.entries) != sch.n_active:
             return None
         entries = []

@@ -67,12 +67,15 @@ class _Layout:
 
 class ModelRunner:
     def __init__(self, model: Model, cache: CacheManager, dtype: torch.dtype, device,
-                 max_tokens: int, max_seqs: int, use_graphs: bool = True):
+                 max_tokens: int, max_seqs: int, use_graphs: bool = True, max_wanted: Optional[int] = None):
+        """`max_wanted`: the most logits rows one step may ask for (default: one per token, which
+        trace replay needs; generation wants one per request and passes max_seqs)."""
         self.model, self.cache = model, cache
         self.dtype, self.device = dtype, torch.device(device)
         self.max_tokens, self.max_seqs = max_tokens, max_seqs
+        self.max_wanted = max_tokens if max_wanted is None else min(max_wanted, max_tokens)
         self.vocab = model.plan.vocab_size
-        self.buffers = Buffers(max_tokens, self.device)
+        self.buffers = Buffers(max_tokens, self.device, self.max_wanted)
         self.layout = _Layout(max_tokens, max_seqs)
         self.dev_meta = torch.zeros(self.layout.total, dtype=torch.int32, device=self.device)
         self._staging = [[torch.zeros(self.layout.total, dtype=torch.int32).pin_memory(), None]
@@ -157,6 +160,8 @@ class ModelRunner:
         N, M, R = len(ids), len(logit), len(entries)
         if N > self.max_tokens:
             raise ValueError(f"{N} tokens exceed the step limit of {self.max_tokens}")
+        if M > self.max_wanted:
+            raise ValueError(f"{M} wanted logits exceed the step limit of {self.max_wanted}")
         if sampling is not None and len(sampling) != M:
             raise ValueError(f"{len(sampling)} sampling entries for {M} wanted logits")
 

@@ -123,10 +123,14 @@ class Scheduler:
         if total > self.max_len:
             raise TooLong(f"prompt is {len(req.ids)} tokens; with {req.max_new_tokens} new it "
                           f"exceeds the {self.max_len}-token row")
-        need = pages_for(total, self.cache.page_size)
         for g in self.cache.groups:
-            if need > g.allocator.num_pages and g.spec.window is None:
-                raise TooLong(f"{total} tokens need {need} pages; the pool has {g.allocator.num_pages}")
+            need = pages_for(total, self.cache.page_size)
+            if g.spec.window is not None:
+                # a windowed group holds the window and the token being written, which may
+                # straddle one page edge more than their count fills
+                need = min(need, pages_for(g.spec.window + 1, self.cache.page_size) + 1)
+            if need > g.allocator.num_pages:
+                raise TooLong(f"{total} tokens need {need} pages at once; the pool has {g.allocator.num_pages}")
         req.sampling.validate()
         self.pending.append(req)
         return req

@@ -6,6 +6,7 @@ which builds an Engine, submits a list of prompts, runs, and prints each output 
 line `wall | tokens | tok/s`.  Here:
 
     MODEL_ID=/path/to/folder python -m socrates_b200.inference_paged
+    python -m socrates_b200.inference_paged --model DIR --prompt "how to make pizza?"
     python -m socrates_b200.inference_paged --model DIR --prompt-ids 5,17,3 --max-new-tokens 32
     python -m socrates_b200.inference_paged --random-config config.json --seed 0 --num-prompts 16
 
@@ -25,6 +26,11 @@ are overridden by the flags:
                      pass                                    model/kernels/__init__.py:36-41
     MAX_BATCH, MAX_LEN, MAX_NEW_TOKENS   the reference's module constants
                                                              model/inference_cont.py:21-23
+
+A folder that holds tokenizer.json is tokenised with its own tokenizer and chat template and
+its outputs are printed as text, as the reference prints them (model/inference_paged.py:67-70,
+139-143, 242-251); a folder without one (random weights) gets a byte tokenizer.  `--num-blocks`
+not given: the page pool is sized from the memory that is free after the weights.
 
 There is no server.
 """
@@ -57,13 +63,13 @@ def main(argv=None) -> int:
     ap.add_argument("--max-len", type=int, default=int(os.environ.get("MAX_LEN", "2048")))
     ap.add_argument("--max-new-tokens", type=int, default=int(os.environ.get("MAX_NEW_TOKENS", "64")))
     ap.add_argument("--block-size", type=int, default=int(os.environ.get("KV_BLOCK", "16")))
-    ap.add_argument("--num-blocks", type=int, default=None, help="pages in the pool (default: max_batch rows of max_len)")
+    ap.add_argument("--num-blocks", type=int, default=None, help="pages in the pool (default: from free memory, at most max_batch rows of max_len)")
     ap.add_argument("--token-budget", type=int, default=2048, help="most tokens one step runs")
     ap.add_argument("--temperature", type=float, default=0.0, help="0 = greedy")
     ap.add_argument("--no-compile", action="store_true", help="no CUDA graphs (same as COMPILE=0)")
     ap.add_argument("--no-warmup", action="store_true",
                     help="record each decode graph at the first step of its width instead of at start-up")
-    ap.add_argument("--prompt", action="append", default=[], help="a text prompt (byte tokenizer); repeatable")
+    ap.add_argument("--prompt", action="append", default=[], help="a text prompt (the folder's tokenizer and chat template, else bytes); repeatable")
     ap.add_argument("--prompt-ids", action="append", default=[], help="a prompt as comma-separated token ids; repeatable")
     ap.add_argument("--num-prompts", type=int, default=0, help="this many random prompts")
     ap.add_argument("--prompt-len", type=int, default=32, help="length of the random prompts")
@@ -81,7 +87,7 @@ def main(argv=None) -> int:
 
     from .config import config_from_dict, load_config
     from .engine.engine import Engine
-    from .engine.tokenizer import ByteTokenizer
+    from .engine.tokenizer import load_tokenizer
     from .weights import write_model_folder
 
     tmp = None
@@ -94,7 +100,7 @@ def main(argv=None) -> int:
         ap.error("give --model DIR (or MODEL_ID=DIR), or --random-config CONFIG.json")
 
     vocab = load_config(model_dir).plan().vocab_size
-    tok = ByteTokenizer(vocab)
+    tok = load_tokenizer(model_dir, vocab)      # the folder's own tokenizer, else bytes
     compile_ = _env_flag("COMPILE") and not args.no_compile
     engine = Engine(model_dir, tok=tok, device=args.device, dtype=args.dtype, compile=compile_,
                     max_batch=args.max_batch, max_len=args.max_len, max_new_tokens=args.max_new_tokens,

@@ -53,7 +53,7 @@ def find_nvcc() -> str:
 
 def _hash(sources: Sequence[Path], flags: Sequence[str]) -> str:
     h = hashlib.sha256()
-    for p in sorted(CSRC.glob("*.cuh")) + list(sources):
+    for p in sorted([*CSRC.glob("*.cuh"), *CSRC.glob("*.h")]) + list(sources):
         h.update(p.name.encode())
         h.update(p.read_bytes())
     h.update(" ".join(flags).encode())

@@ -60,7 +60,7 @@ class LMHead(Part):
         return [self.linear.weight]
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
-        return self.linear(ctx, x, "logits", out="float32")
+        return self.linear(ctx, x, "logits", out="wanted_float32")
 
 
 register_part("embedding", "embedding", Embedding)

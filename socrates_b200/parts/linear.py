@@ -22,6 +22,7 @@ class Linear:
 
     def __call__(self, ctx, x: torch.Tensor, buffer: str, out: str = "model", epilogue: int = 0) -> torch.Tensor:
         """`out`: "model" -> [M, N] in the model dtype; "float32" -> [M, N] float32;
+        "wanted_float32" -> the same for rows that are wanted logits (a buffer of its own size);
         "partial" -> float32 [S, M, N]; "model_or_partial" -> partial sums when the
         product is cut along K (the weight-streaming regime), else the model dtype: for
         consumers that can add the parts themselves."""
@@ -33,6 +34,8 @@ class Linear:
             y = ctx.buffers.take(buffer, M, (N,), ctx.dtype)
         elif out == "float32":
             y = ctx.buffers.take(buffer, M, (N,), torch.float32)
+        elif out == "wanted_float32":
+            y = ctx.buffers.take_wanted(buffer, M, (N,), torch.float32)
         elif out == "partial":
             S = ctx.gemm_splits(M, self.weight, x.dtype)
             y = ctx.buffers.take_flat(buffer, S * M * N, torch.float32).view(S, M, N)

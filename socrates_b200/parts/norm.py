@@ -37,7 +37,8 @@ class RMSNorm(Part):
         is left unchanged.
         """
         M = stream.residual.shape[0] if row_index is None else row_index.numel()
-        out = ctx.buffers.take(buffer, M, (self.dim,), ctx.dtype)
+        take = ctx.buffers.take if row_index is None else ctx.buffers.take_wanted
+        out = take(buffer, M, (self.dim,), ctx.dtype)
         delta = stream.pending.partial if stream.pending is not None else None
         ops.add_rmsnorm(stream.residual, delta, self.gain, out, self.eps, row_index)
         if row_index is None:

@@ -9,10 +9,12 @@ It imports the reference's dense-cache model (model/qwen/qwen_kv_cont.py Qwen3, 
 masks `k_pos <= position` and therefore also handles a prompt fed in portions), loads
 the random weights of tiny models A and B0 into it (for the untied B0 the reference
 has no lm_head: its final-norm output is hooked and multiplied with lm_head here),
-feeds one sequence whole, and writes `golden_<name>.pt` with the token ids, a checksum
-of the weights and the reference's float32 logits at a few positions.  The test
-tests/test_plain.py::test_plain_matches_reference_golden recomputes those logits with
-the plain implementation.  The reference's code is only imported and run, never copied.
+feeds one sequence whole, and writes `golden_<name>.pt` with the configuration, the
+token ids and the reference's float32 logits at a few positions, and
+`golden_<name>.safetensors` with the very weights it ran (a few hundred KB), so that
+the comparison does not depend on which random numbers this machine's torch draws.  The
+test tests/test_plain.py::test_plain_matches_reference_golden recomputes those logits
+with the plain implementation.  The reference's code is only imported and run, never copied.
 """
 
 import hashlib
@@ -71,7 +73,9 @@ def main():
         mine = plain.logits(w, cfg, ids[0].tolist(), torch.float32)
         print(name, "max |plain - reference| =", (mine - logits).abs().max().item(),
               "max |reference| =", logits.abs().max().item())
-        torch.save({"ids": ids[0].tolist(), "positions": keep, "logits": logits[keep].clone(),
+        from safetensors.torch import save_file
+        save_file({k: v.contiguous() for k, v in w.items()}, str(out_dir / f"golden_{name}.safetensors"))
+        torch.save({"config": cfg, "ids": ids[0].tolist(), "positions": keep, "logits": logits[keep].clone(),
                     "weights_sha256": weights_checksum(w)}, out_dir / f"golden_{name}.pt")
 
 

@@ -1,5 +1,6 @@
 """What bench.py answers without a GPU: more than one GPU is refused with one line and exit
-code 2, and the reference arm says why it cannot run."""
+code 2, and the reference arm answers with one JSON line and exit code 0 (its numbers where
+a GPU and the reference's copy are present, else the reason)."""
 
 import json
 import subprocess
@@ -20,8 +21,9 @@ def test_more_than_one_gpu_is_refused_with_one_line():
     assert len(lines) == 1 and "one GPU" in lines[0]
 
 
-def test_reference_arm_is_unavailable_and_says_why():
+def test_reference_arm_prints_one_json_line():
     r = run("--impl", "reference", "--gpus", "1", "--steps", "4", "--warmup", "3")
-    assert r.returncode == 0
+    assert r.returncode == 0, r.stderr[-2000:]
     line = json.loads(r.stdout.strip().splitlines()[-1])
-    assert line["impl"] == "reference" and "hatchling" in line["unavailable"]
+    assert line["impl"] == "reference"
+    assert ("unavailable" in line and line["unavailable"]) or line["value"] > 0

@@ -231,6 +231,29 @@ def test_command_line(tmp_path):
     assert "> hello" in proc.stdout
 
 
+def test_command_line_with_the_folders_tokenizer(tmp_path):
+    """A model folder that carries tokenizer.json: text goes in through its chat template and
+    text comes out (the 8 words of the test's tokenizer, never bare ids)."""
+    import subprocess
+    import sys
+    from test_tokenizer import WORDS, write_tokenizer
+    folder = make_folder(tmp_path, "A")
+    write_tokenizer(folder)
+    root = __import__("pathlib").Path(__file__).resolve().parent.parent
+    proc = subprocess.run([sys.executable, "-m", "socrates_b200.inference_paged", "--model", str(folder),
+                           "--prompt", "hello world", "--prompt", "how are you", "--max-new-tokens", "6",
+                           "--max-len", "64", "--max-batch", "2", "--dtype", "float32"], cwd=str(root),
+                          capture_output=True, text=True, timeout=300, env={**__import__("os").environ,
+                                                                            "HF_HUB_OFFLINE": "1"})
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = proc.stdout.splitlines()
+    assert "> hello world" in lines and "> how are you" in lines
+    out = lines[lines.index("> hello world") + 1]
+    # ids above the tokenizer's 8 words decode to nothing, ids within to words: never digits
+    assert not any(ch.isdigit() for ch in out), out
+    assert all(w in WORDS for w in out.split()), out
+
+
 def test_entry_point_guards(tmp_path):
     from socrates_b200 import Engine, TooLong
     folder = make_folder(tmp_path, "A")

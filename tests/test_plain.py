@@ -23,12 +23,20 @@ def _checksum(w):
 @pytest.mark.parametrize("name", ["A", "B0"])
 def test_plain_matches_reference_golden(tmp_path, name):
     """Logits of the reference's own model classes (stored by tests/golden/make_golden.py)."""
+    from safetensors import safe_open
     gold = torch.load(GOLDEN / f"golden_{name}.pt")
-    cfg, w = plain.load_folder(make_folder(tmp_path, name))
-    if _checksum(w) != gold["weights_sha256"]:
-        pytest.skip("this torch draws other random weights than the one that made the golden file")
+    cfg, w = gold["config"], {}
+    with safe_open(str(GOLDEN / f"golden_{name}.safetensors"), framework="pt") as f:
+        for k in f.keys():
+            w[k] = f.get_tensor(k)
+    assert _checksum(w) == gold["weights_sha256"]              # the weights the reference ran
     mine = plain.logits(w, cfg, gold["ids"], torch.float32)[gold["positions"]]
     assert torch.allclose(mine, gold["logits"], atol=2e-6, rtol=1e-5)
+    # and the framework's seeded writer still makes these weights on this machine, or says so
+    _, fresh = plain.load_folder(make_folder(tmp_path, name))
+    if _checksum(fresh) != gold["weights_sha256"]:
+        import warnings
+        warnings.warn("this torch draws other random weights than the one that made the golden files")
 
 
 def test_rms_norm_formula():

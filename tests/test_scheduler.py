@@ -24,8 +24,11 @@ def next_token(seq):
 class FakeEngine:
     """Runs plans without a GPU: checks what is fed against what the cache holds."""
 
-    def __init__(self, num_pages=64, max_batch=4, max_len=256, budget=32, window=None, max_queue=100):
+    def __init__(self, num_pages=64, max_batch=4, max_len=256, budget=32, window=None, max_queue=100,
+                 only_windowed=False):
         needs = [CacheNeeds(PagedKVSpec(1, 16, None)), CacheNeeds(PagedKVSpec(1, 16, window))]
+        if only_windowed:
+            needs = needs[1:]
         self.cache = CacheManager(needs, max_batch, max_len, 16, num_pages, torch.float32, "cpu")
         self.s = Scheduler(self.cache, max_batch, max_len, budget, max_queue, stop_ids=[STOP])
         self.fed = {}                     # request id -> tokens the "cache" holds for its current row
@@ -155,6 +158,20 @@ def test_door_checks():
         e.submit([1], 1)
     with pytest.raises(ValueError):
         FakeEngine().s.submit(Request(ids=[], max_new_tokens=1))
+
+
+def test_windowed_pool_too_small_is_refused_at_the_door():
+    """A windowed group needs the window and the token being written at once, which can straddle
+    one page edge more than their count fills: 32 + 1 tokens in 16-slot pages are up to 4 pages.
+    A pool one page short is refused at submit, not found out in the middle of generation."""
+    small = FakeEngine(num_pages=3, window=32, only_windowed=True, max_batch=1)
+    with pytest.raises(TooLong):
+        small.submit([3] * 100, 20)
+    small.submit([3] * 20, 8)                                  # 28 tokens never fill the window: 2 pages
+    enough = FakeEngine(num_pages=4, window=32, only_windowed=True, max_batch=1)
+    r = enough.submit([3 + (i % 40) for i in range(100)], 20)
+    enough.run()
+    assert r.done and enough.cache.free_pages() == [4]
 
 
 def test_cancel_frees_the_row():

@@ -54,9 +54,13 @@ def test_no_alloc_entry_point_matches_the_regular_one_twice():
     from socrates_b200.kernels.library import library
     require_kernels()
     lib = library()
-    # two different problems in a row: the second finds the scratch array used
+    # Two different problems in a row, both with more than four partitions, so that both go
+    # through the scratch array (up to four merge inside a thread-block cluster and never
+    # touch it): the second finds another problem's (m, l, o) at the same offsets, with other
+    # lengths, head counts and head size, and has a one-page row whose later partitions are
+    # empty.  A partition slot that a call read without writing it first would show.
     for (lens, Hq, Hkv, D, NP, window, seed) in (([700, 65, 16, 300], 8, 2, 64, 5, 0, 1),
-                                                  ([33, 1, 257], 32, 8, 128, 3, 37, 2)):
+                                                  ([33, 1, 257, 900, 9], 32, 8, 128, 6, 37, 2)):
         q, k, v, table, rows, pos = case(lens, Hq, Hkv, D, seed)
         N = len(lens)
         scale = D ** -0.5
