@@ -18,10 +18,22 @@ reference's stock path:
 `value` is timed with CUDA events around K calls of decode_step(); `e2e` is the wall
 clock around K more calls (each call already holds the host-to-device copies and the
 read-back of the tokens).
+
+Two settings are not the reference's defaults, both through its own switches:
+
+  * PAGED_PARTITION=128.  Its "auto" rule (model/kernels/__init__.py:36-41) takes one pass
+    over the whole row from 64 (row, KV head) blocks on, and the one-pass kernel keeps
+    group x row-length floats in shared memory and refuses more than 47 KB
+    (model/kernels/csrc/paged_attention.cu:301-315): 8,192-token rows at batch 8 are
+    refused.  128 is the split size its auto rule uses whenever it splits.
+  * COMPILE.  The measurement runs in a child process.  If the child dies with
+    torch.compile on (the reference's default), the parent records how, and runs it once
+    more with the reference's COMPILE=0; the printed line says which one it is.
 """
 
 import json
 import os
+import subprocess
 import sys
 import time
 from pathlib import Path
@@ -60,19 +72,44 @@ class PromptTable:
         return " ".join(str(i) for i in ids)
 
 
-def run(args, cfg_dict, shape_name, layers_full, ClockSampler, peaks, arithmetic):
+def run(args, argv):
+    """Parent: runs the measurement in a child process (`bench.py --impl reference` with
+    SOCRATES_REFERENCE_CHILD set), first as the reference ships (COMPILE=1), then, if that child
+    dies, with the reference's own COMPILE=0.  Prints the child's line, or why there is none."""
     if not (REF_ROOT / "model" / "inference_paged.py").exists():
         return unavailable("baseline/_ref holds no copy of the reference (baseline/install_reference.py "
                            "makes it where the reference's source tree is present)")
+    import torch
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device")
+    failures = []
+    for compile_flag in ("1", "0"):
+        env = dict(os.environ, SOCRATES_REFERENCE_CHILD="1", COMPILE=compile_flag, DEVICE="cuda",
+                   HF_HUB_OFFLINE="1", PYTHONFAULTHANDLER="1")
+        env.setdefault("PAGED_PARTITION", "128")
+        proc = subprocess.run([sys.executable, *argv], env=env, capture_output=True, text=True)
+        lines = [l for l in proc.stdout.splitlines() if l.startswith("{")]
+        if proc.returncode == 0 and lines:
+            line = json.loads(lines[-1])
+            if failures:
+                line.setdefault("notes", {})["earlier_attempts"] = failures
+            print(json.dumps(line))
+            return 0
+        tail = " | ".join(proc.stderr.strip().splitlines()[-6:])
+        failures.append(f"COMPILE={compile_flag}: exit code {proc.returncode}: {tail}"[:600])
+        sys.stderr.write(proc.stderr[-4000:])
+    return unavailable("the reference engine did not finish the workload: " + " || ".join(failures))
+
+
+def measure(args, cfg_dict, shape_name, layers_full, ClockSampler, peaks, arithmetic):
+    """Child: builds the reference's engine and times it (see the module docstring)."""
     os.environ.setdefault("HF_HUB_OFFLINE", "1")
     os.environ["DEVICE"] = "cuda"
     sys.path.insert(0, str(REF_ROOT))
     import torch
 
-    if not torch.cuda.is_available():
-        return unavailable("no CUDA device")
     torch.cuda.set_device(0)
-    notes = {}
+    notes = {"paged_partition": os.environ.get("PAGED_PARTITION", "auto")}
     import glob
     built = glob.glob(str(REF_ROOT / "model" / "kernels" / "_C*.so"))
     if not built:
@@ -114,14 +151,8 @@ def run(args, cfg_dict, shape_name, layers_full, ClockSampler, peaks, arithmetic
 
     from model.inference_cont import COMPILE
     t_build = time.perf_counter()
-    try:
-        engine = make(COMPILE)
-        notes["compile"] = bool(COMPILE)
-    except Exception as e:                                   # noqa: BLE001
-        notes["compile"] = False
-        notes["compile_error"] = " ".join(f"{type(e).__name__}: {e}".split())[:200]
-        torch.cuda.synchronize()
-        engine = make(False)
+    engine = make(COMPILE)
+    notes["compile"] = bool(COMPILE)
     notes["startup_s"] = round(time.perf_counter() - t_build, 1)
 
     decode_bytes, prefill_flops = arithmetic(cfg_dict, cfg["num_hidden_layers"])
@@ -200,6 +231,7 @@ def run(args, cfg_dict, shape_name, layers_full, ClockSampler, peaks, arithmetic
                    "tied_head": True, "global_batch": B, "seq_len": ctx, "max_len": max_len,
                    "page_size": page, "parallelism": "single GPU",
                    "torch_compile": notes["compile"], "attn_impl": os.environ.get("ATTN_IMPL", "auto"),
+                   "paged_partition": notes["paged_partition"],
                    "l2": "inputs larger than L2 (weights 8 GB per step)", "peaks": pk["source"]},
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",

@@ -421,9 +421,11 @@ def main():
     if args.impl == "reference":
         sys.path.insert(0, str(ROOT / "baseline"))
         import reference_arm
+        if os.environ.get("SOCRATES_REFERENCE_CHILD") != "1":
+            return reference_arm.run(args, [str(Path(__file__).resolve()), *sys.argv[1:]])
         layers = args.layers or cfg_full["num_hidden_layers"]
-        return reference_arm.run(args, dict(cfg_full, num_hidden_layers=layers), name,
-                                 cfg_full["num_hidden_layers"], ClockSampler, peaks, arithmetic)
+        return reference_arm.measure(args, dict(cfg_full, num_hidden_layers=layers), name,
+                                     cfg_full["num_hidden_layers"], ClockSampler, peaks, arithmetic)
     if workload == "serve":
         return run_serve(args, name, cfg_full)
     return run_decode(args, name, cfg_full)
