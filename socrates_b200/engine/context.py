@@ -17,17 +17,6 @@ import torch
 from ..kernels import ops
 
 
-def _paged_partition() -> Optional[int]:
-    """PAGED_PARTITION: None for "auto" (or unset), else keys per attention partition (0: no split)."""
-    v = os.environ.get("PAGED_PARTITION", "auto").strip().lower()
-    if v in ("", "auto"):
-        return None
-    n = int(v)
-    if n < 0:
-        raise ValueError(f"PAGED_PARTITION must be 'auto' or a non-negative integer, not {v!r}")
-    return n
-
-
 def _l2_prefetch_budget() -> int:
     """Bytes of the next product's weights that a weight-streaming product asks for in L2 once
     its own loads are issued (`SOCRATES_L2_PREFETCH_MB`, 0 turns it off).  Measured on the 4B
@@ -75,14 +64,16 @@ class Buffers:
             self._by_name[key] = buf
         return buf[:rows]
 
-    def take_flat(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+    def take_flat(self, name: str, numel: int, dtype: torch.dtype, zeroed: bool = False) -> torch.Tensor:
+        """`zeroed`: the storage is zero when it is allocated (for counters that kernels leave at
+        zero after every use); it is not cleared again on later calls."""
         key = (name, dtype)
         buf = self._flat.get(key)
         if buf is None or buf.numel() < numel:
             if buf is not None:
                 self._retired.append(buf)
             size = max(numel, 2 * buf.numel() if buf is not None else numel)
-            buf = torch.empty(size, dtype=dtype, device=self.device)
+            buf = (torch.zeros if zeroed else torch.empty)(size, dtype=dtype, device=self.device)
             self._flat[key] = buf
         return buf[:numel]
 
@@ -181,57 +172,3 @@ class StepContext:
         if nxt is None or self.l2_prefetch_bytes <= 0 or not nxt.is_contiguous():
             return None
         return (nxt, self.l2_prefetch_bytes)
-
-    def attention_partitions(self, num_kv_heads: int, blocks_per_sm: int, keys_per_part: int) -> int:
-        """Into how many key partitions each query's keys are cut.
-
-        A function of static quantities only (batch width, limits), so that a recorded
-        graph stays valid: as many partitions as keep every block resident at once (one
-        wave, no tail), at most 16, never less than `keys_per_part` keys of the longest
-        possible row in a partition.
-        """
-        most = max(1, -(-self.max_context // keys_per_part))
-        fixed = _paged_partition()
-        if fixed is not None:
-            # PAGED_PARTITION as in the reference (model/kernels/__init__.py:23-41): keys per
-            # partition, 0 = one pass over all keys; "auto" or unset = the rule below
-            return 1 if fixed == 0 else max(1, min(-(-self.max_context // fixed), 64))
-        blocks = max(1, num_kv_heads * self.num_tokens)
-        want = (self.num_sms * blocks_per_sm) // blocks
-        return max(1, min(want, most, 16))
-
-    def attention(self, out, q, k_pool, v_pool, table, num_heads: int, scale: float, window: int) -> None:
-        """Causal attention of every token of the step over its row's pages.
-
-        bfloat16 with a head size and group size the tensor-core kernels take: the
-        split-key decode kernel (mma.sync) when every request brings one token, else the
-        tile kernel: tcgen05 for head sizes 64 and 128, mma.sync for 16 and 32;
-        everything else (the float32 engine above all) runs on the SIMT kernel.
-        """
-        Hkv, page_size, D = k_pool.shape[1], k_pool.shape[2], k_pool.shape[3]
-        N = q.shape[0]
-        tensor_cores = q.dtype == torch.bfloat16
-        if (tensor_cores and not self.all_decode and self.status is not None
-                and ops.attention_tcgen05_supports(num_heads, Hkv, D, page_size)):
-            ops.attention_prefill_tcgen05(out, q, k_pool, v_pool, table, self.seq_starts, self.seq_rows,
-                                          self.seq_first_pos, num_heads, scale, self.status, window)
-            return
-        if tensor_cores and not self.all_decode and ops.attention_mma_supports(num_heads, Hkv, D, page_size, False):
-            ops.attention_prefill_mma(out, q, k_pool, v_pool, table, self.seq_starts, self.seq_rows,
-                                      self.seq_first_pos, num_heads, scale, window)
-            return
-        use_mma = tensor_cores and self.all_decode and ops.attention_mma_supports(num_heads, Hkv, D, page_size, True)
-        if use_mma:
-            NP = self.attention_partitions(Hkv, ops.attention_decode_mma_blocks_per_sm(D), 128)
-        else:
-            NP = self.attention_partitions(Hkv, 4, 4 * page_size)
-        part_o = part_ml = None
-        if NP > 1:
-            part_o = self.buffers.take_flat("attn_part_o", N * num_heads * NP * D, torch.float32)
-            part_ml = self.buffers.take_flat("attn_part_ml", N * num_heads * NP * 2, torch.float32)
-        if use_mma:
-            ops.attention_decode_mma(out, q, k_pool, v_pool, table, self.token_rows, self.positions, num_heads,
-                                     scale, window, NP, part_o, part_ml)
-        else:
-            ops.attention_simt(out, q, k_pool, v_pool, table, self.token_rows, self.positions, num_heads,
-                               scale, window, NP, part_o, part_ml)

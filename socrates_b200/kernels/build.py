@@ -32,7 +32,8 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
 
 # Sources of the core library, in link order.
 CORE_SOURCES = ["errors.cu", "elementwise.cu", "sampling.cu", "gemm_simt.cu", "attention_simt.cu",
-                "gemm_tcgen05.cu", "gemm_tcgen05_rows.cu", "attention_mma.cu", "attention_tcgen05.cu"]
+                "gemm_tcgen05.cu", "gemm_tcgen05_rows.cu", "attention_mma.cu", "attention_decode.cu",
+                "attention_tcgen05.cu"]
 
 
 class BuildError(RuntimeError):

@@ -42,6 +42,8 @@ _SIGNATURES = {
     "sb_attention_decode_mma": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P],
     "sb_attention_decode_mma_blocks_per_sm": [I, I],
     "sb_attention_decode_mma_kernels": [I],
+    "sb_attention_decode_stream_supports": [I, I, I, I],
+    "sb_attention_decode_stream": [P, P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, I, P],
     "sb_attention_tcgen05_supports": [I, I, I, I],
     "sb_attention_prefill_tcgen05": [P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P],
 }

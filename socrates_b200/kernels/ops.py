@@ -348,6 +348,53 @@ def attention_decode_mma(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
         kernels=lib.sb_attention_decode_mma_kernels(num_partitions))
 
 
+def attention_decode_stream_supports(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Whether the streaming decode kernel takes this shape (bfloat16; head sizes 16 to 128, groups
+    of up to 16 query heads, pages of at least 16 slots)."""
+    return bool(library().sb_attention_decode_stream_supports(num_heads, num_kv_heads, head_dim, page_size))
+
+
+def attention_decode_stream(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                            block_table: torch.Tensor, token_rows: torch.Tensor, positions: torch.Tensor,
+                            num_heads: int, scale: float, window: int, chunk_keys: int, max_chunks: int,
+                            part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
+                            counters: Optional[torch.Tensor] = None, variant: int = 0) -> None:
+    """Paged attention of single decode tokens (bfloat16) as one persistent kernel whose warps
+    stream fixed chunks of `chunk_keys` keys (a multiple of 16) of each (token, KV head); a row's
+    chunks lie at fixed key positions, so its numbers do not depend on the rest of the batch.
+
+    `max_chunks` bounds the chunks the visible keys of any token span.  Scratch for max_chunks > 1:
+    part_o float32 with N*Hq*max_chunks*D elements, part_ml with N*Hq*max_chunks*2, and int32
+    `counters` with N*Hkv entries that are zero before the first call (the kernel leaves them zero).
+
+    The kernel reads the block table, rows, positions and the keys and values below each
+    position before it waits for the kernel that precedes it on the stream: those must be
+    older than that kernel (a host copy, an earlier step)."""
+    N = q.shape[0]
+    _, Hkv, BS, D = k_pool.shape
+    Hq = num_heads
+    _want(q, "q", torch.bfloat16, (N, Hq * D))
+    _want(out, "out", torch.bfloat16, (N, Hq * D))
+    _want(k_pool, "k_pool", torch.bfloat16)
+    _want(v_pool, "v_pool", torch.bfloat16, k_pool.shape)
+    _want(block_table, "block_table", torch.int32)
+    _want(token_rows, "token_rows", torch.int32, (N,))
+    _want(positions, "positions", torch.int32, (N,))
+    if max_chunks > 1:
+        _want(part_o, "part_o", torch.float32)
+        _want(part_ml, "part_ml", torch.float32)
+        _want(counters, "counters", torch.int32)
+        if (part_o.numel() < N * Hq * max_chunks * D or part_ml.numel() < N * Hq * max_chunks * 2
+                or counters.numel() < N * Hkv):
+            raise KernelError("attention scratch buffers are too small")
+    lib = library()
+    check(lib, lib.sb_attention_decode_stream(
+        _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(counters), _ptr(q), _ptr(k_pool), _ptr(v_pool),
+        _ptr(block_table), block_table.shape[1], _ptr(token_rows), _ptr(positions), N, Hq, Hkv, D, BS,
+        int(window), float(scale), int(chunk_keys), int(max_chunks), int(variant), _stream()),
+        "attention_decode_stream")
+
+
 def attention_decode_mma_blocks_per_sm(head_dim: int, variant: int = 0) -> int:
     """Blocks of the decode attention kernel that are resident on one SM at a time."""
     return library().sb_attention_decode_mma_blocks_per_sm(int(head_dim), int(variant))

@@ -3,8 +3,9 @@
 The same sequences are replayed whole; most of them in one step and the last 32 tokens
 one by one; in portions of changing size down to two tokens; and mixed, up to four
 live requests with portions of some beside decoded tokens of others, in a pool so
-small that pages are used again.  Both tiny configurations, float32 and bfloat16.
-Every position's logits are compared.
+small that pages are used again.  Both tiny configurations and B without its window (the
+shape on which the plain implementation is checked against the reference's own output),
+float32 and bfloat16.  Every position's logits are compared.
 """
 
 import numpy as np
@@ -12,7 +13,7 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from tiny_configs import CONFIGS, make_folder
+from tiny_configs import ALL_CONFIGS as CONFIGS, make_folder
 from traces import Trace, compare, first_wrong, last_decoded, mixed, portions, run_trace, whole
 
 pytestmark = pytest.mark.gpu
@@ -21,7 +22,7 @@ pytestmark = pytest.mark.gpu
 # reference's own model-level tolerance is 1e-4 (tests/test_paged_model.py:35-76).
 # bfloat16: activations are rounded to 8 bits of mantissa about ten times a layer.
 TOL = {"float32": 1e-4, "bfloat16": 2e-2}
-LENGTHS = {"A": [70, 131, 203], "B": [65, 150, 301]}
+LENGTHS = {"A": [70, 131, 203], "B": [65, 150, 301], "B0": [65, 150, 301]}
 
 
 def sequences(name):
@@ -31,7 +32,7 @@ def sequences(name):
             for i, n in enumerate(LENGTHS[name])}
 
 
-@pytest.fixture(scope="module", params=[(c, d) for c in ("A", "B") for d in ("float32", "bfloat16")],
+@pytest.fixture(scope="module", params=[(c, d) for c in ("A", "B", "B0") for d in ("float32", "bfloat16")],
                 ids=lambda p: f"{p[0]}-{p[1]}")
 def replayed(request, tmp_path_factory):
     name, dtype = request.param

@@ -194,6 +194,46 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path, dtype, tol):
         unregister_architecture(ToyConfig.architecture)
 
 
+def test_toy_mixer_with_state_through_the_entry_point(tmp_path):
+    """The same mixer through Engine with running ahead switched on.  A step that is launched
+    early and then dropped would advance the state slots a second time when it is run again, so
+    the engine must not run ahead for a model that keeps per-request state.  Requests of
+    different lengths end at different steps (each end would drop an early step); every produced
+    token is checked against the whole-sequence statement."""
+    from safetensors.torch import load_file
+    from socrates_b200 import Engine
+    from socrates_b200.config import register_architecture, unregister_architecture
+    from socrates_b200.parts import register_part, unregister_part
+    from socrates_b200.weights import write_model_folder
+
+    register_part("mixer", "toy_decay", make_toy())
+    register_architecture(ToyConfig.architecture, ToyConfig)
+    try:
+        folder = write_model_folder(ToyConfig(0.9), seed=4, out_dir=tmp_path / "toy")
+        w = load_file(str(folder / "model.safetensors"))
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(0, VOCAB, (n,), generator=g).tolist() for n in (9, 21, 4, 15)]
+        new = [12, 5, 17, 8]
+        eng = Engine(str(folder), device="cuda:0", dtype="float32", max_batch=3, max_len=64, max_new_tokens=20,
+                     token_budget=16, run_ahead=True)
+        reqs = [eng.submit(p, max_new_tokens=n) for p, n in zip(prompts, new)]
+        while eng.scheduler.has_work():
+            assert eng.step()
+            eng.scheduler.check()
+        assert eng.ahead_launched == 0                       # state slots: no step is launched early
+        for p, n, r in zip(prompts, new, reqs):
+            assert r.done and len(r.output) == n
+            logits = plain_toy(w, list(p) + r.output[:-1], 0.9)
+            scale = float(logits.abs().max())
+            for i, tok in enumerate(r.output):
+                row = logits[len(p) - 1 + i]
+                best = int(torch.argmax(row))
+                assert tok == best or float(row[best] - row[tok]) <= 1e-4 * scale, (i, tok, best)
+    finally:
+        unregister_part("mixer", "toy_decay")
+        unregister_architecture(ToyConfig.architecture)
+
+
 # ------------------------------------------------------------------------------------------
 # A feed-forward with routing and another position encoding, defined here.
 

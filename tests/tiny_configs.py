@@ -32,11 +32,12 @@ TINY_B = copy.deepcopy(TINY_B0)
 TINY_B.update({"sliding_window": 37, "use_sliding_window": True, "max_window_layers": 1})
 
 CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1)}      # name -> (config.json content, seed)
+ALL_CONFIGS = dict(CONFIGS, B0=(TINY_B0, 1))        # B0: what the reference's own classes can run
 
 
 def make_folder(tmp_path, name):
     """Write the tiny model `name` with random weights into tmp_path/name; returns the folder."""
     from socrates_b200.config import config_from_dict
     from socrates_b200.weights import write_model_folder
-    cfg_dict, seed = CONFIGS[name] if name in CONFIGS else ({"B0": TINY_B0}[name], 1)
+    cfg_dict, seed = ALL_CONFIGS[name]
     return write_model_folder(config_from_dict(cfg_dict), seed, tmp_path / name)
