@@ -99,6 +99,9 @@ namespace sb {
 // The kernels for many rows (gemm_tcgen05_rows.cu).  0, a cudaError_t or SB_ERR_ARG.
 int gemm_tcgen05_many_rows(const void* A, const void* W, void* C, int M, int N, int K, int c_dtype, int* status,
                            int variant, int epi, cudaStream_t stream);
+// The pair kernel in equal shares of K blocks (gemm_tcgen05_rows.cu): float32 [parts, M, N].
+int gemm_tcgen05_shares_parts(int M, int N, int K);
+int gemm_tcgen05_shares(const void* A, const void* W, float* C, int M, int N, int K, int* status, cudaStream_t stream);
 }  // namespace sb
 
 namespace {
@@ -446,7 +449,9 @@ int dispatch(const void* A, const void* W, void* C, int M, int N, int K, int spl
 // variant: 0 = the kernels chosen by shape; 4 = one tile per block also for many rows
 //          (the default there is the persistent kernel); 128, 160, 256 = that tile width
 //          in the persistent kernel instead of the one it would choose; 1128, 1160, 1192,
-//          1256 = the pair kernel (two SMs per tile, cta_group::2) with tiles 256 x (variant - 1000).
+//          1256 = the pair kernel (two SMs per tile, cta_group::2) with tiles 256 x (variant - 1000);
+//          2000 = the pair kernel dealing equal shares of K blocks, float32 partial sums
+//          [parts, M, N] with *splits_io == sb_gemm_tcgen05_shares_parts(M, N, K).
 // epilogue: 0 = C[M,N]; 1 = W interleaves gate and up rows and C is [M, N/2] = up * silu(gate)
 //          (no K split; for many rows N >= 128).
 // next_weights / next_bytes: null / 0, or a 16-byte aligned range that the product after this
@@ -467,6 +472,16 @@ extern "C" int sb_gemm_tcgen05(void* C, const void* A, const void* W, int M, int
     SB_REQUIRE((M + 127) / 128 <= 65535 && (N + 63) / 64 <= 65535, "gemm_tcgen05: matrix too large");
     SB_REQUIRE(next_bytes >= 0 && (reinterpret_cast<uintptr_t>(next_weights) & 15) == 0,
                "gemm_tcgen05: the next-weights hint must be 16-byte aligned");
+    if (variant == 2000) {
+        // many rows as float32 partial sums from the pair kernel in equal shares of K blocks
+        const int parts = sb::gemm_tcgen05_shares_parts(M, N, K);
+        SB_REQUIRE(parts > 0 && c_dtype == SB_F32 && epilogue == 0 && splits == parts,
+                   "gemm_tcgen05: equal shares need float32 output of %d parts (asked: %d) for M=%d N=%d K=%d",
+                   parts, splits, M, N, K);
+        const int rc = sb::gemm_tcgen05_shares(A, W, static_cast<float*>(C), M, N, K, status, stream);
+        if (rc != 0) return rc;
+        SB_LAUNCH_CHECK();
+    }
     g_next.ptr = static_cast<const uint8_t*>(next_weights);
     g_next.bytes = next_weights != nullptr ? (next_bytes & ~15LL) : 0;
     int rc;
@@ -479,6 +494,13 @@ extern "C" int sb_gemm_tcgen05(void* C, const void* A, const void* W, int M, int
     g_next = NextWeights{};
     if (rc != 0) return rc;
     SB_LAUNCH_CHECK();
+}
+
+// How many float32 parts variant 2000 (the pair kernel in equal shares of K blocks) writes for this
+// shape; 0 if it does not serve it (few rows, a narrow N, more than four pieces to a tile).
+extern "C" int sb_gemm_tcgen05_shares_parts(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0 || K % 8) return 0;
+    return sb::gemm_tcgen05_shares_parts(M, N, K);
 }
 
 // How many K parts sb_gemm_tcgen05 will actually write for a wanted count (host only).

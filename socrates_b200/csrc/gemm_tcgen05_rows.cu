@@ -172,7 +172,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const 
             const int a0 = (t % tiles_m) * BM, b0 = (t / tiles_m) * BN;
             const int m = a0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_d + acc * ACC_STRIDE + (static_cast<uint32_t>(quarter * 32) << 16);
-            drain_tile<BN, TC, EPI, (ISSUERS == 2 ? BN : 0)>(taddr, C, M, N, m, b0);
+            if constexpr (sizeof(TC) == 4 && EPI == 0 && BN % 32 == 0) {
+                float* stage = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)) +
+                                                        STAGES * stage_bytes<BN>() + quarter * kStageBytesPerWarp);
+                drain_tile_f32_staged<BN, (ISSUERS == 2 ? BN : 0)>(taddr, reinterpret_cast<float*>(C), M, N,
+                                                                    a0 + quarter * 32, lane, b0, stage);
+            } else {
+                drain_tile<BN, TC, EPI, (ISSUERS == 2 ? BN : 0)>(taddr, C, M, N, m, b0);
+            }
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -424,7 +431,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
             const int a0 = (t % tiles_m) * 256 + (int)rank * BM, b0 = (t / tiles_m) * BN;
             const int m = a0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_d + acc * ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
-            drain_tile<BN, TC, EPI>(taddr, C, M, N, m, b0);
+            if constexpr (sizeof(TC) == 4 && EPI == 0 && BN % 32 == 0) {
+                float* stage = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)) + STAGES * SB +
+                                                        quarter * kStageBytesPerWarp);
+                drain_tile_f32_staged<BN>(taddr, reinterpret_cast<float*>(C), M, N, a0 + quarter * 32, lane, b0, stage);
+            } else {
+                drain_tile<BN, TC, EPI>(taddr, C, M, N, m, b0);
+            }
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&acc_empty[acc]), 0));
@@ -441,13 +454,239 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     }
 }
 
+// ----------------------------------------------------------------------------- pair kernel, equal shares
+// The pair kernel with the work dealt in equal shares of (tile, K block) units instead of whole
+// tiles: pair p takes units [total * p / pairs, total * (p + 1) / pairs) of the tiles' K blocks
+// laid end to end (tiles in the order of the pair kernel, row index fastest).  Where a share
+// ends inside a tile, the tile's K range is finished by the next pair.  Nothing is handed over
+// between pairs: the output is float32 partial sums [parts, M, N], as the products with few
+// rows write them, and the consumer (the norm that folds a branch into the residual) adds the
+// parts in their fixed order.  A piece of a tile that starts at K block 0 writes part 0; a piece
+// that starts later writes part (its pair - the pair that owns the tile's first unit); the piece
+// that ends a tile also writes zeros to the parts the tile did not use.
+// Why: at 2,048 rows a narrow projection has 80 tiles of 256 x 256 for 74 pairs: whole tiles take
+// two waves of which the second is 8 % full; equal shares take 1.08 waves' worth of time.
+struct Piece {
+    int tile, kb0, kb1, part;
+    bool ends_tile;
+};
+struct PieceWalk {
+    long long u, u_end, total;
+    int kb_total, pair, n_pairs;
+    __device__ PieceWalk(int pair_, int n_pairs_, int n_tiles, int kb_total_)
+        : total((long long)n_tiles * kb_total_), kb_total(kb_total_), pair(pair_), n_pairs(n_pairs_) {
+        u = total * pair / n_pairs;
+        u_end = total * (pair + 1) / n_pairs;
+    }
+    // the next piece of this pair's share; false when the share is done
+    __device__ bool next(Piece& pc) {
+        if (u >= u_end) return false;
+        pc.tile = (int)(u / kb_total);
+        pc.kb0 = (int)(u - (long long)pc.tile * kb_total);
+        const long long left = u_end - u;
+        pc.kb1 = (int)min((long long)kb_total, pc.kb0 + left);
+        pc.ends_tile = pc.kb1 == kb_total;
+        if (pc.kb0 == 0) {
+            pc.part = 0;
+        } else {
+            // the pair that owns unit x is ((x + 1) * pairs - 1) / total
+            const long long first = (long long)pc.tile * kb_total;
+            pc.part = pair - (int)(((first + 1) * n_pairs - 1) / total);
+        }
+        u += pc.kb1 - pc.kb0;
+        return true;
+    }
+};
+
+template <int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_tcgen05_pair_shares_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                                float* __restrict__ C, int M, int N, int K, int tiles_m, int tiles_n, int parts,
+                                int* __restrict__ status) {
+    constexpr int BN = 256;
+    constexpr int ACC_COLS = 256;
+    constexpr int SB = pair_stage_bytes<BN>();
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[STAGES];
+    __shared__ __align__(8) uint64_t acc_full[2];
+    __shared__ __align__(8) uint64_t acc_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int kb_total = (K + BK - 1) / BK;
+    const int n_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&acc_full[a]), 1);
+            mbar_init(smem_u32(&acc_empty[a]), 8);      // four epilogue warps in each block of the pair
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(2 * ACC_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                    // both blocks' barriers exist from here on
+    tcgen05_fence_after();
+    const uint32_t tmem_d = tmem_base_slot;
+    uint32_t peer_base;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];"
+                 : "=r"(peer_base) : "r"(map_to_cta(smem_u32(&tmem_base_slot), rank ^ 1u)) : "memory");
+    const bool bases_agree = peer_base == tmem_d;
+    if (!bases_agree && threadIdx.x == 0) atomicExch(status, 4);
+    sb::pdl_launch_dependents();
+
+    if (!bases_agree) {
+        // nothing is computed; fall through to the common exit
+    } else if (warp == 0 && lane == 0) {
+        // ---------------- producer (in both blocks): this block's halves of the A and B tiles
+        uint32_t it = 0;
+        bool waited = false, ok = true;
+        PieceWalk walk(pair, n_pairs, n_tiles, kb_total);
+        Piece pc;
+        while (ok && walk.next(pc)) {
+            const int a0 = (pc.tile % tiles_m) * 256 + (int)rank * BM;
+            const int b0 = (pc.tile / tiles_m) * BN + (int)rank * (BN / 2);
+            int i = pc.kb0;
+            if (!waited) {
+                // weights first (nobody writes them), the activations after the wait on the previous kernel
+                const int ahead = min(pc.kb1 - pc.kb0, STAGES);
+                for (int q = 0; q < ahead; ++q) {
+                    if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[q]), 2 * SB);
+                    tma_load_2d_pair(tiles + q * SB + BM * BK * 2, &tma_b, map_to_cta(smem_u32(&full_bar[q]), 0),
+                                     (pc.kb0 + q) * BK, b0);
+                }
+                sb::pdl_wait();
+                waited = true;
+                for (int q = 0; q < ahead; ++q)
+                    tma_load_2d_pair(tiles + q * SB, &tma_a, map_to_cta(smem_u32(&full_bar[q]), 0), (pc.kb0 + q) * BK, a0);
+                i = pc.kb0 + ahead;
+                it = ahead;
+            }
+            for (; i < pc.kb1 && ok; ++i, ++it) {
+                const int s = it % STAGES;
+                if (it >= STAGES && !mbar_wait(smem_u32(&empty_bar[s]), ((it / STAGES) - 1) & 1)) { ok = false; break; }
+                if (*((volatile int*)&abort_flag)) { ok = false; break; }
+                const uint32_t bar0 = map_to_cta(smem_u32(&full_bar[s]), 0);
+                if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[s]), 2 * SB);
+                tma_load_2d_pair(tiles + s * SB, &tma_a, bar0, i * BK, a0);
+                tma_load_2d_pair(tiles + s * SB + BM * BK * 2, &tma_b, bar0, i * BK, b0);
+            }
+        }
+        if (!ok) {
+            atomicExch(status, 1);
+            atomicExch(&abort_flag, 1);
+            if (rank == 0) {
+                for (uint32_t q = it > STAGES ? it - STAGES : 0; q < it; ++q)
+                    mbar_wait(smem_u32(&full_bar[q % STAGES]), (q / STAGES) & 1);
+            } else {
+                const unsigned long long t0 = global_timer_ns();
+                while (global_timer_ns() - t0 < 1000000ull) {}
+            }
+        }
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ---------------- MMA issuer: one thread of block 0 for the pair
+        constexpr uint32_t idesc = make_idesc_pair(BN);
+        uint32_t it = 0;
+        int j = 0;
+        bool ok = true;
+        PieceWalk walk(pair, n_pairs, n_tiles, kb_total);
+        Piece pc;
+        for (; ok && walk.next(pc); ++j) {
+            const int acc = j & 1;
+            if (j >= 2 && !mbar_wait_cluster(smem_u32(&acc_empty[acc]), ((j >> 1) - 1) & 1)) { ok = false; break; }
+            tcgen05_fence_after();
+            const uint32_t d = tmem_d + acc * ACC_COLS;
+            for (int i = pc.kb0; i < pc.kb1; ++i, ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(smem_u32(&full_bar[s]), (it / STAGES) & 1)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t sa = tiles + s * SB;
+                const uint32_t sb_ = sa + BM * BK * 2;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    tcgen05_mma_bf16_pair(d, make_smem_desc(sa + k * UMMA_K * 2), make_smem_desc(sb_ + k * UMMA_K * 2),
+                                          idesc, (i > pc.kb0 || k > 0) ? 1u : 0u);
+                tcgen05_commit_pair(smem_u32(&empty_bar[s]));        // frees the stage in both blocks
+            }
+            if (!ok) break;
+            tcgen05_commit_pair(smem_u32(&acc_full[acc]));           // both blocks' epilogues may read
+        }
+        if (!ok) {
+            atomicExch(status, 2);
+            atomicExch(&abort_flag, 1);
+        }
+    } else if (warp >= 2) {
+        // ---------------- epilogue (in both blocks): warp w owns TMEM lanes 32*(w%4) .. +31
+        sb::pdl_wait();                                    // C may still be read by an earlier kernel until now
+        const int quarter = warp & 3;
+        const size_t part_stride = (size_t)M * N;
+        int j = 0;
+        PieceWalk walk(pair, n_pairs, n_tiles, kb_total);
+        Piece pc;
+        for (; walk.next(pc); ++j) {
+            const int acc = j & 1;
+            bool good = mbar_wait(smem_u32(&acc_full[acc]), (j >> 1) & 1);
+            if (*((volatile int*)&abort_flag)) good = false;
+            good = __all_sync(0xffffffffu, good);
+            if (!good) {
+                if (lane == 0) { atomicExch(status, 3); atomicExch(&abort_flag, 1); }
+                break;
+            }
+            tcgen05_fence_after();
+            const int a0 = (pc.tile % tiles_m) * 256 + (int)rank * BM, b0 = (pc.tile / tiles_m) * BN;
+            const int m = a0 + quarter * 32 + lane;
+            const uint32_t taddr = tmem_d + acc * ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
+            float* stage = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)) + STAGES * SB +
+                                                    quarter * kStageBytesPerWarp);
+            drain_tile_f32_staged<BN>(taddr, C + (size_t)pc.part * part_stride, M, N, a0 + quarter * 32, lane, b0, stage);
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+            if (pc.ends_tile && m < M) {
+                // the parts this tile did not use count as zero
+                for (int z = pc.part + 1; z < parts; ++z) {
+                    float* row = C + (size_t)z * part_stride + (size_t)m * N + b0;
+                    const int cols = min(BN, N - b0);
+                    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0 && cols % 4 == 0) {
+                        for (int c = 0; c < cols; c += 4) *reinterpret_cast<float4*>(row + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+                    } else {
+                        for (int c = 0; c < cols; ++c) row[c] = 0.f;
+                    }
+                }
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(2 * ACC_COLS)
+                     : "memory");
+    }
+}
+
 using sb::get_map;
 
 template <int BN, int STAGES, typename TC, int EPI, int ISSUERS>
 int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, int K, int* status,
                       cudaStream_t stream) {
     auto kernel = gemm_tcgen05_persistent_kernel<BN, STAGES, TC, EPI, ISSUERS>;
-    constexpr int smem = STAGES * stage_bytes<BN>() + 1024;
+    constexpr int smem = STAGES * stage_bytes<BN>() + 1024 + kStageBytes;
     static sb::OncePerDevice once_per_device;
     bool& configured = once_per_device.flag();
     static int num_sms = 0;
@@ -470,7 +709,7 @@ template <int BN, int STAGES, typename TC, int EPI>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, int K, int* status,
                 cudaStream_t stream) {
     auto kernel = gemm_tcgen05_pair_kernel<BN, STAGES, TC, EPI>;
-    constexpr int smem = STAGES * pair_stage_bytes<BN>() + 1024;
+    constexpr int smem = STAGES * pair_stage_bytes<BN>() + 1024 + kStageBytes;
     static sb::OncePerDevice once_per_device;
     bool& configured = once_per_device.flag();
     static int max_pairs = 0;
@@ -506,14 +745,14 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, in
 // Tile widths of the pair kernel and their ring depths.
 #define SB_PAIR_WIDTHS(X) X(256) X(192) X(160) X(128)
 constexpr int pair_stages(int bn) {
-    const int s = (222 * 1024) / (BM * BK * 2 + (bn / 2) * BK * 2);
+    const int s = (222 * 1024 - kStageBytes) / (BM * BK * 2 + (bn / 2) * BK * 2);
     return s > 8 ? 8 : s;
 }
 
 // Tile widths of the persistent kernel, and the ring depth that fits in shared memory for each.
 #define SB_PERSISTENT_WIDTHS(X) X(256) X(160) X(128)
 constexpr int persistent_stages(int bn) {
-    const int s = (222 * 1024) / (BM * BK * 2 + bn * BK * 2);
+    const int s = (222 * 1024 - kStageBytes) / (BM * BK * 2 + bn * BK * 2);
     return s > 6 ? 6 : s;
 }
 
@@ -583,7 +822,79 @@ int many_rows(const void* A, const void* W, void* C, int M, int N, int K, int* s
     }
 }
 
+
+// How many pairs of blocks the GPU holds at once for the equal-shares kernel (0 if none fits).
+int shares_pairs() {
+    static sb::OncePerDevice once_per_device;
+    static int max_pairs = 0;
+    bool& configured = once_per_device.flag();
+    if (!configured) {
+        auto kernel = gemm_tcgen05_pair_shares_kernel<pair_stages(256)>;
+        constexpr int smem = pair_stages(256) * pair_stage_bytes<256>() + 1024 + kStageBytes;
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2, 1, 1);
+        cfg.blockDim = dim3(192, 1, 1);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&max_pairs, kernel, &cfg) != cudaSuccess) max_pairs = 0;
+        configured = true;
+    }
+    return max_pairs;
+}
+
+// Parts that the equal-shares kernel writes for this shape with `pairs` pairs: a tile of kb_total
+// K blocks is cut by at most ceil((kb_total - 1) / smallest share) share ends.
+int shares_parts(int M, int N, int K, int pairs) {
+    const long long n_tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
+    const int kb_total = (K + BK - 1) / BK;
+    if (pairs < 1 || n_tiles < 1) return 0;
+    const long long smallest = n_tiles * kb_total / pairs;
+    if (smallest < 1) return 0;
+    return (int)((kb_total - 1 + smallest - 1) / smallest) + 1;
+}
+
 }  // namespace
+
+namespace sb {
+// The pair kernel in equal shares of K blocks: float32 partial sums C [parts, M, N] with
+// parts = gemm_tcgen05_shares_parts(M, N, K) (0: this shape is not served).
+int gemm_tcgen05_shares_parts(int M, int N, int K) {
+    if (M <= 256 || N < 256 || K < BK) return 0;
+    const long long n_tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
+    const int pairs = (int)min((long long)shares_pairs(), n_tiles * ((K + BK - 1) / BK));
+    const int parts = shares_parts(M, N, K, pairs);
+    return parts >= 1 && parts <= 4 ? parts : 0;
+}
+
+int gemm_tcgen05_shares(const void* A, const void* W, float* C, int M, int N, int K, int* status,
+                        cudaStream_t stream) {
+    const int parts = gemm_tcgen05_shares_parts(M, N, K);
+    if (parts == 0) {
+        sb_set_error("gemm_tcgen05: the equal-shares kernel does not serve M=%d N=%d K=%d", M, N, K);
+        return SB_ERR_ARG;
+    }
+    CUtensorMap ma, mb;
+    if (!get_map(&ma, A, M, K, BM) || !get_map(&mb, W, N, K, 128)) {
+        sb_set_error("gemm_tcgen05: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d)", M, N, K);
+        return SB_ERR_ARG;
+    }
+    const int tiles_m = (M + 255) / 256, tiles_n = (N + 255) / 256;
+    const long long units = (long long)tiles_m * tiles_n * ((K + BK - 1) / BK);
+    const int pairs = (int)min((long long)shares_pairs(), units);
+    auto kernel = gemm_tcgen05_pair_shares_kernel<pair_stages(256)>;
+    constexpr int smem = pair_stages(256) * pair_stage_bytes<256>() + 1024 + kStageBytes;
+    sb::launch_cluster(kernel, dim3(2 * pairs), dim3(192), smem, stream, dim3(2, 1, 1), ma, mb, C, M, N, K, tiles_m,
+                       tiles_n, parts, status);
+    return 0;
+}
+}  // namespace sb
 
 namespace sb {
 // Products with many rows (prompt portions), no K split, N >= 128: the persistent kernel or,

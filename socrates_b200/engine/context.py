@@ -126,8 +126,10 @@ class StepContext:
         return (x_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0
                 and self.status is not None)
 
-    def gemm_splits(self, M: int, w: torch.Tensor, x_dtype: torch.dtype) -> int:
-        """Into how many K parts a product whose output is partial sums is cut.
+    def gemm_splits(self, M: int, w: torch.Tensor, x_dtype: torch.dtype, shares: bool = True) -> int:
+        """Into how many K parts a product whose output is partial sums is cut.  `shares` = False:
+        the caller would rather have one part in the model dtype than the float32 parts of the
+        equal-shares kernel (whose gain the wider output would eat).
 
         The weight-streaming regime (M <= 64) is cut into enough blocks to keep two resident
         on every SM, at least two K blocks of 64 each; a product with many rows only where its
@@ -138,6 +140,9 @@ class StepContext:
             return 1
         N, K = w.shape
         if M > 64:
+            parts = self.gemm_shares(M, w, x_dtype) if shares else 0
+            if parts:
+                return parts
             # Many rows but few tiles (a short prompt portion through a narrow projection): cut K
             # so that the tiles cover the SMs.  Measured on the 4B shape at 512 rows: o 29 -> 20 us,
             # down 57 -> 33 us with three parts; from 1,024 rows on a cut no longer pays.
@@ -150,6 +155,35 @@ class StepContext:
         most = max(1, (-(-K // 64)) // 2)
         return ops.gemm_tcgen05_splits(K, min(want, most, 16))
 
+    def gemm_shares(self, M: int, w: torch.Tensor, x_dtype: torch.dtype) -> int:
+        """Parts of the pair kernel in equal shares of K blocks if a product of M rows whose output
+        is partial sums should run on it, else 0.  Whole tiles run in waves over the SMs; a product
+        whose last wave is mostly empty (a 2,048-row portion through a 2,560-wide projection: 80
+        tiles of 256 x 256 for 74 pairs, 256 tiles of 128 x 160 for 148 SMs) loses up to half of
+        its time there.  Chosen when the model of the kernels' measured costs per K block (690
+        clocks for a pair's 256 x 256 tile; 540 + 0.94 * width for one SM's 128 x width tile) says
+        that equal shares take less than 0.9 of the best whole-tile choice, and both operands
+        together stay well inside the L2 cache (96 MB): whole tiles run the row tiles of a weight
+        panel side by side, so the panel comes from memory once, while equal shares shift every
+        pair to another K offset and rely on the cache to keep what an earlier pair fetched
+        (measured at 2,048 rows: 2,560 x 9,728, 90 MB of operands, 94 against 116 us; 5,120 x
+        25,600, 367 MB, 525 against 469 us).  Shapes alone decide."""
+        if not self.uses_tensor_cores(x_dtype, w) or os.environ.get("SOCRATES_GEMM_SHARES", "1") == "0":
+            return 0
+        N, K = w.shape
+        if (M + N) * K * 2 > 96 * (1 << 20):
+            return 0
+        parts = ops.gemm_tcgen05_shares_parts(M, N, K)
+        if parts == 0:
+            return 0
+        pairs = max(1, self.num_sms // 2)
+        shares_cost = (-(-M // 256) * -(-N // 256)) * 690.0 / pairs
+        rows128 = -(-M // 128)
+        whole_cost = min((-(-(rows128 * -(-N // bn)) // self.num_sms)) * (540.0 + 0.94 * bn) for bn in (256, 160, 128))
+        if M >= 4096:       # the pair kernel with whole tiles is the choice there
+            whole_cost = min(whole_cost, (-(-(-(-M // 256) * -(-N // 256)) // pairs)) * 690.0)
+        return parts if shares_cost < 0.9 * whole_cost else 0
+
     def can_fuse_silu_mul(self, M: int, w: torch.Tensor, x_dtype: torch.dtype) -> bool:
         """Whether the product with an interleaved gate/up matrix can apply SiLU*mul in its
         epilogue (the tensor-core kernels do, for few rows and for many)."""
@@ -160,6 +194,10 @@ class StepContext:
         can_fuse_silu_mul) out is [M, N/2] = up * silu(gate) of interleaved columns."""
         S = out.shape[0] if out.dim() == 3 else 1
         if self.uses_tensor_cores(x.dtype, w):
+            M = x.shape[0]
+            if M > 64 and out.dim() == 3 and epilogue == 0 and S == self.gemm_shares(M, w, x.dtype) and S > 0:
+                ops.gemm_tcgen05(out, x, w, self.status, S, variant=ops.SHARES_VARIANT)
+                return
             ops.gemm_tcgen05(out if out.dim() == 3 and S > 1 else out.view(out.shape[-2], out.shape[-1]),
                              x, w, self.status, S, epilogue=epilogue, prefetch=self._next_weights(w))
         else:

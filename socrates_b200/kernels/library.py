@@ -37,6 +37,7 @@ _SIGNATURES = {
     "sb_attention_simt": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P],
     "sb_gemm_tcgen05": [P, P, P, I, I, I, I, P, P, I, I, P, LL, P],
     "sb_gemm_tcgen05_splits": [I, I],
+    "sb_gemm_tcgen05_shares_parts": [I, I, I],
     "sb_attention_mma_supports": [I, I, I, I, I],
     "sb_attention_prefill_mma": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],
     "sb_attention_decode_mma": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P],

@@ -235,6 +235,17 @@ def gemm_tcgen05_splits(K: int, splits: int) -> int:
     return library().sb_gemm_tcgen05_splits(int(K), int(splits))
 
 
+SHARES_VARIANT = 2000      # gemm_tcgen05 variant: the pair kernel dealing equal shares of K blocks
+
+
+def gemm_tcgen05_shares_parts(M: int, N: int, K: int) -> int:
+    """How many float32 parts `gemm_tcgen05(..., variant=SHARES_VARIANT)` writes for this shape: the
+    pair kernel (two SMs per 256 x 256 tile) with the tiles' K blocks dealt to the pairs in equal
+    shares, a tile that a share's end cuts being finished by the next pair into another part.
+    0: the shape is not served (few rows, N below 256, more than four pieces to a tile)."""
+    return int(library().sb_gemm_tcgen05_shares_parts(int(M), int(N), int(K)))
+
+
 def gemm_tcgen05(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, status: torch.Tensor,
                  splits: int = 1, variant: int = 0, epilogue: int = 0,
                  prefetch: Optional[Tuple[torch.Tensor, int]] = None) -> int:
@@ -252,7 +263,9 @@ def gemm_tcgen05(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, status: to
     _want(a, "a", torch.bfloat16)
     _want(w, "w", torch.bfloat16, (N, K))
     _want(status, "status", torch.int32)
-    S = gemm_tcgen05_splits(K, splits)
+    S = gemm_tcgen05_shares_parts(M, N, K) if variant == SHARES_VARIANT else gemm_tcgen05_splits(K, splits)
+    if variant == SHARES_VARIANT and (S == 0 or out.dim() != 3):
+        raise KernelError(f"the equal-shares kernel does not serve M={M} N={N} K={K} (or out is not [S, M, N])")
     if out.dim() == 2:
         if S != 1:
             raise KernelError("a split product needs a float32 [S, M, N] output")

@@ -29,7 +29,7 @@ class Linear:
         M = x.shape[0]
         N = self.out_features // 2 if epilogue == 1 else self.out_features
         if out == "model_or_partial":
-            out = "partial" if ctx.gemm_splits(M, self.weight, x.dtype) > 1 else "model"
+            out = "partial" if ctx.gemm_splits(M, self.weight, x.dtype, shares=False) > 1 else "model"
         if out == "model":
             y = ctx.buffers.take(buffer, M, (N,), ctx.dtype)
         elif out == "float32":

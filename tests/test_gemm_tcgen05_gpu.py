@@ -171,6 +171,50 @@ def test_gemm_tcgen05_pair_kernel_is_the_choice_for_many_rows(ops):
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(2048, 2560, 4096), (2048, 2560, 9728), (2048, 5120, 8192), (1024, 2560, 4096),
+                                   (1999, 2500, 1000), (8192, 2560, 512), (300, 6144, 2560)])
+def test_gemm_tcgen05_equal_shares(ops, M, N, K):
+    """The pair kernel dealing equal shares of K blocks: the parts add up to the product; a tile
+    that one pair finishes alone has zeros in the other parts; a second call into a buffer full of
+    NaN gives the same bits (every element of every part is written).  Shapes: the narrow
+    projections of the 4B and 32B widths at 2,048 rows, fewer tiles than pairs (three pieces to a
+    tile), ragged rows, columns and K."""
+    a, w, want = operands(M, N, K, seed=2)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    S = ops.gemm_tcgen05_shares_parts(M, N, K)
+    assert 1 <= S <= 4
+    out = torch.full((S, M, N), float("nan"), dtype=torch.float32, device=DEV)
+    assert ops.gemm_tcgen05(out, a, w, status, S, variant=ops.SHARES_VARIANT) == S
+    assert int(status.item()) == 0
+    assert torch.isfinite(out).all()
+    close(out.double().sum(0), want, K, False)
+    again = torch.full_like(out, float("nan"))
+    ops.gemm_tcgen05(again, a, w, status, S, variant=ops.SHARES_VARIANT)
+    assert torch.equal(again, out)
+
+
+def test_equal_shares_are_chosen_for_the_narrow_projections_of_a_long_portion(ops):
+    """The step context's choice: 2,048 rows through o and down of the 4B widths run as equal
+    shares (two parts); the wide products and short portions do not."""
+    from socrates_b200.engine.context import Buffers, StepContext
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    ctx = StepContext(torch.bfloat16, torch.device(DEV), Buffers(64, DEV), 1, 1, None, None, None, None, None, None,
+                      None, all_decode=False, max_context=1, num_sms=sms,
+                      status=torch.zeros(1, dtype=torch.int32, device=DEV))
+    shape = lambda n, k: torch.empty(n, k, dtype=torch.bfloat16, device=DEV)
+    if sms == 148:
+        assert ctx.gemm_splits(2048, shape(2560, 4096), torch.bfloat16) == 2
+        assert ctx.gemm_splits(2048, shape(2560, 9728), torch.bfloat16) == 2
+        assert ctx.gemm_splits(2048, shape(6144, 2560), torch.bfloat16, shares=False) == 1
+        assert ctx.gemm_shares(128, shape(2560, 4096), torch.bfloat16) == 0
+    a, wt, want = operands(2048, 2560, 4096, seed=3)
+    S = ctx.gemm_splits(2048, wt, torch.bfloat16)
+    out = torch.full((S, 2048, 2560), float("nan"), dtype=torch.float32, device=DEV)
+    ctx.gemm(out, a, wt)
+    close(out.double().sum(0), want, 4096, False)
+    assert int(ctx.status.item()) == 0
+
+
 @pytest.mark.parametrize("M,F,K", [(200, 320, 96), (2048, 9728, 256), (65, 64, 64), (300, 203, 72),
                                    (8, 9728, 2560), (1, 80, 64), (64, 203, 72), (17, 64, 96)])
 def test_gemm_tcgen05_fused_silu_mul(ops, M, F, K):
