@@ -3,6 +3,7 @@
 import json
 
 import pytest
+import torch
 
 from socrates_b200.config import (ConfigError, Qwen3Config, config_from_dict, known_architectures,
                                   load_config, register_architecture, unregister_architecture)
@@ -84,3 +85,23 @@ def test_register_another_architecture():
             register_architecture("OtherForCausalLM", Other)
     finally:
         unregister_architecture("OtherForCausalLM")
+
+
+def test_page_pool_from_memory():
+    """`num_blocks=None`: pages from the memory that is free after the weights, never more than
+    every row at full length, never fewer than one row needs; an explicit number is kept."""
+    from socrates_b200.cache import CacheManager, CacheNeeds, PagedKVSpec
+    from socrates_b200.config import EngineConfig
+    cfg = EngineConfig(max_batch=64, max_len=8192, block_size=16)
+    full = 64 * 512
+    # the 32B shape: 64 layers of 8 KV heads of 128, bfloat16 -> 256 KiB a token, 4 MiB a page
+    needs = [CacheNeeds(PagedKVSpec(8, 128, None)) for _ in range(64)]
+    per_page = CacheManager.bytes_per_page(needs, 16, torch.bfloat16)
+    assert per_page == 64 * 2 * 8 * 16 * 128 * 2
+    assert cfg.pages_from_memory(10 ** 15, per_page) == full               # memory is no limit: the worst case
+    got = cfg.pages_from_memory(110 * 2 ** 30, per_page)                   # 110 GiB free beside the weights
+    assert got == int(110 * 2 ** 30 * 0.9) // per_page and 512 <= got < full
+    assert cfg.pages_from_memory(1, per_page) == 512                       # at least one row
+    assert EngineConfig(num_blocks=77).pages_from_memory(10 ** 15, per_page) == 77
+    with pytest.raises(ValueError):
+        EngineConfig(kv_memory_fraction=0.0).validate()
