@@ -78,7 +78,7 @@ def paged_attention(ctx, out, q, k_pool, v_pool, table, num_heads: int, scale: f
             return
     fixed = paged_partition()
     take = ctx.buffers.take_flat
-    if (bf16 and ctx.all_decode and fixed is not None
+    if (bf16 and ctx.all_decode and fixed is not None and N <= 1024      # the kernel's limit of tokens a launch
             and ops.attention_decode_stream_supports(num_heads, Hkv, D, page_size)):
         chunk = max(16, -(-(fixed if fixed > 0 else max_len) // 16) * 16)
         span = min(max_len, window) if window else max_len
