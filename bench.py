@@ -370,7 +370,7 @@ def run_serve(args, name, cfg_full):
         "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02), token ids uniform over the vocabulary, seeded arrivals",
         "config": dict(shape_config(name, cfg_full, layers), global_batch=64, seq_len="128..4096 prompt",
-                       max_len=8192, page_size=16, parallelism="single GPU", cuda_graph=True,
+                       max_len=8192, page_size=16, parallelism="single GPU",
                        requests=n, rate_per_s=args.rate, max_new=max_new,
                        pool_pages=engine.cache.groups[0].allocator.num_pages, peaks=pk["source"]),
         "clocks": sampler.summary(t0, t1), "gpu_launches": runner.kernel_launches - before, "impl": "ours",
