@@ -250,6 +250,8 @@ def run_decode(args, name, cfg_full):
         pms = sorted(times)[len(times) // 2]
         prefill = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
                    "frac": round(prefill_flops(T) / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        if "bf16_tflops_sustained" in pk:      # the rate cuBLAS holds for seconds under the power cap
+            prefill["frac_of_sustained"] = round(prefill_flops(T) / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
 
     e2e = None
     if not args.skip_e2e:
