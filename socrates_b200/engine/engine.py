@@ -125,9 +125,11 @@ class Engine:
 
     # ------------------------------------------------------------------ requests
     def submit(self, prompt: Union[str, Sequence[int]], max_new_tokens: Optional[int] = None,
-               temperature: float = 0.0, seed: int = 0) -> Request:
+               temperature: float = 0.0, seed: int = 0, stream: bool = False) -> Request:
         """Queue a prompt (token ids, or text if the engine has a tokenizer).
-        Raises QueueFull or TooLong as the reference does (model/inference_paged.py:132-148)."""
+        Raises QueueFull or TooLong as the reference does (model/inference_paged.py:132-148).
+        `stream`: the request gets a thread-safe queue `req.stream` that receives each token as
+        it is produced and None at the end (the reference's `stream` flag, :132-138)."""
         text = None
         if isinstance(prompt, str):
             if self.tok is None:
@@ -142,6 +144,9 @@ class Engine:
                 raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
         req = Request(ids=ids, max_new_tokens=max_new_tokens or self.max_new_tokens,
                       sampling=SamplingParams(float(temperature), int(seed)), prompt=text)
+        if stream:
+            import queue
+            req.stream = queue.Queue()
         return self.scheduler.submit(req)
 
     # ------------------------------------------------------------------ stepping

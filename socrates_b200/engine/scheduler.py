@@ -25,6 +25,7 @@ the cancelled flag, retire + compaction + refill in the same iteration.  Changed
 
 from __future__ import annotations
 
+import queue
 import threading
 import time
 from collections import deque
@@ -60,6 +61,10 @@ class Request:
     first_token: float = 0.0
     finished: float = 0.0
     event: threading.Event = field(default_factory=threading.Event)
+    # a queue that receives every produced token and None at the end (the reference's req.stream,
+    # model/inference_paged.py:136-138, 196-198, is an asyncio queue fed from the serve thread; this
+    # one is thread-safe and needs no event loop)
+    stream: Optional["queue.Queue"] = None
     # scheduler state
     cached: int = 0            # tokens of ids + output that are in the cache
     preemptions: int = 0
@@ -168,10 +173,19 @@ class Scheduler:
         self.n_active -= 1
         req.row = -1
 
+    @staticmethod
+    def _drop(req: Request) -> None:
+        """A request that was cancelled before it got a row."""
+        if req.stream is not None:
+            req.stream.put(None)
+        req.event.set()
+
     def retire(self, req: Request) -> None:
         self._vacate(req)
         if not req.finished:
             req.finished = time.perf_counter()
+        if req.stream is not None:
+            req.stream.put(None)            # the end of the stream, for a finished and for a cancelled request
         req.event.set()
 
     def preempt(self, req: Request) -> None:
@@ -212,7 +226,7 @@ class Scheduler:
         portion is sized; in the batch the decode tokens come first.
         """
         while self.pending and self.pending[0].cancelled:
-            self.pending.popleft().event.set()
+            self._drop(self.pending.popleft())
         self.sweep()
         planned: List[PlannedEntry] = []
         preempted: List[Request] = []
@@ -233,7 +247,7 @@ class Scheduler:
         while self.pending and self.n_active < self.max_batch and prefill_budget >= 1:
             req = self.pending[0]
             if req.cancelled:
-                self.pending.popleft().event.set()
+                self._drop(self.pending.popleft())
                 continue
             if req in preempted:
                 break                       # it just gave up its pages: not in this step
@@ -306,6 +320,8 @@ class Scheduler:
         else:
             req.output.append(token)
             self.output_tokens += 1
+            if req.stream is not None:
+                req.stream.put(token)
             if len(req.output) >= req.max_new_tokens:
                 req.done = True
         if req.done:

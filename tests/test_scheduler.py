@@ -174,6 +174,27 @@ def test_windowed_pool_too_small_is_refused_at_the_door():
     assert r.done and enough.cache.free_pages() == [4]
 
 
+def test_stream_receives_every_token_and_the_end():
+    import queue
+    e = FakeEngine()
+    a = e.submit([4, 9, 2], 6)
+    b = e.submit([7] * 20, 9)
+    c = e.submit([11, 12], 5)
+    for r in (a, b, c):
+        r.stream = queue.Queue()
+    e.step()
+    c.cancelled = True                                     # a cancelled request's stream ends too
+    e.run()
+    for r in (a, b, c):
+        got = []
+        while True:
+            item = r.stream.get_nowait()
+            if item is None:
+                break
+            got.append(item)
+        assert got == r.output and r.stream.empty()
+
+
 def test_cancel_frees_the_row():
     e = FakeEngine()
     a, b = e.submit([1, 2, 3], 50), e.submit([4, 5, 6], 50)
