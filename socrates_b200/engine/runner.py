@@ -269,13 +269,14 @@ class ModelRunner:
                                f"the step's results are not valid")
 
     def _run(self, ctx: StepContext, M: int, sample: bool):
-        logits = self.model.forward(ctx, self.cache)
-        tokens = None
-        if sample and M:
-            L, m = self.layout, self.dev_meta
-            tokens = self.sampled[:M]
-            ops.sample(tokens, logits, m[L.temp:L.temp + M].view(torch.float32),
-                       m[L.seed:L.seed + M], m[L.counter:L.counter + M], self.sample_scratch)
+        with ops.stream_scope():            # one stream look-up for the step's kernels (also while a graph records)
+            logits = self.model.forward(ctx, self.cache)
+            tokens = None
+            if sample and M:
+                L, m = self.layout, self.dev_meta
+                tokens = self.sampled[:M]
+                ops.sample(tokens, logits, m[L.temp:L.temp + M].view(torch.float32),
+                           m[L.seed:L.seed + M], m[L.counter:L.counter + M], self.sample_scratch)
         return logits, tokens
 
     def prepare(self, entries: Sequence[StepEntry],

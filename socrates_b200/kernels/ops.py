@@ -27,11 +27,33 @@ def _code(dtype: torch.dtype) -> int:
 
 
 def _ptr(t: Optional[torch.Tensor]):
-    return None if t is None else ctypes.c_void_p(t.data_ptr())
+    """The tensor's device address as ctypes takes it for a pointer argument (an int; None = null)."""
+    return None if t is None else t.data_ptr()
+
+
+_scoped_stream = None      # the stream handle inside a stream_scope, else None
+
+
+class stream_scope:
+    """Inside the scope every kernel of this module goes to the stream that was current when the
+    scope was entered, looked up once.  `torch.cuda.current_stream()` costs several microseconds a
+    call, which with some 330 launches was a quarter of the host's time for a step; a step's
+    kernels all go to one stream anyway.  The caller must not switch streams inside the scope."""
+
+    def __enter__(self):
+        global _scoped_stream
+        self._outer = _scoped_stream
+        _scoped_stream = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global _scoped_stream
+        _scoped_stream = self._outer
+        return False
 
 
 def _stream():
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return _scoped_stream if _scoped_stream is not None else torch.cuda.current_stream().cuda_stream
 
 
 def _want(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
@@ -41,7 +63,7 @@ def _want(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
         raise KernelError(f"{name} must be contiguous")
     if dtype is not None and t.dtype != dtype:
         raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
-    if shape is not None and tuple(t.shape) != tuple(shape):
+    if shape is not None and t.shape != shape:              # torch.Size compares with tuples
         raise KernelError(f"{name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
 
 
