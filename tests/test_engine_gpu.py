@@ -273,6 +273,44 @@ def test_decoded_logits_do_not_depend_on_the_batch(tmp_path, monkeypatch, dtype,
     assert torch.equal(alone, beside)
 
 
+def test_page_pressure_at_real_widths():
+    """Two layers at the Qwen3-4B widths, 60 requests of 16 to 1,500 tokens submitted at once into 16
+    rows and a pool of 260 pages (4,160 tokens): portions beside decode tokens, many preemptions and
+    recomputations, greedy and temperature requests mixed.  Every request gets exactly its tokens,
+    the bookkeeping holds throughout, every page comes back, and the same run again gives the same
+    tokens (nothing depends on timing or on what a reused page held)."""
+    import random
+    from socrates_b200 import Engine
+    from socrates_b200.config import config_from_dict
+    from socrates_b200.engine.engine import build_random_model
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "vocab_size": 4096, "hidden_size": 2560, "intermediate_size": 9728,
+           "num_hidden_layers": 2, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+           "rms_norm_eps": 1e-6, "rope_theta": 1e6, "tie_word_embeddings": True}
+    built = build_random_model(config_from_dict(cfg), 0, torch.bfloat16, torch.device("cuda:0"))
+    outs = []
+    for _ in range(2):
+        eng = Engine(built, device="cuda:0", dtype="bfloat16", max_batch=16, max_len=2048, max_new_tokens=64,
+                     block_size=16, num_blocks=260, token_budget=512)
+        rng = random.Random(1)
+        g = torch.Generator().manual_seed(1)
+        reqs = []
+        for i in range(60):
+            p = torch.randint(1, 4096, (rng.randint(16, 1500),), generator=g).tolist()
+            reqs.append(eng.submit(p, max_new_tokens=rng.randint(4, 64), temperature=0.7 if i % 3 else 0.0, seed=i))
+        steps = 0
+        while eng.scheduler.has_work():
+            assert eng.step()
+            steps += 1
+            if steps % 25 == 0:
+                eng.scheduler.check()
+        eng.scheduler.check()
+        assert all(r.done and len(r.output) == r.max_new_tokens for r in reqs)
+        assert eng.scheduler.preemptions > 10
+        assert eng.cache.free_pages() == [260]
+        outs.append([r.output for r in reqs])
+    assert outs[0] == outs[1]
+
+
 def test_first_tokens_of_a_sequence(tmp_path):
     """Positions 0 and 1 alone: one-token and two-token prompts, and a first portion of one token."""
     from socrates_b200.engine.runner import StepEntry
