@@ -210,14 +210,30 @@ def test_cancel_frees_the_row():
 
 
 def test_pages_run_out_latest_request_is_preempted_and_recomputed():
-    """Three pages: the older request holds one, the newer two.  When the older one
-    needs a second page the newer one gives up its pages, goes back to the front of the
-    queue, is recomputed later, and still produces exactly its own tokens."""
+    """Four pages, two requests of one page each that grow to three: both are admitted (there
+    is room for the newer one's prompt and a page to spare for the older), both take a second
+    page, and when the older one needs its third the newer one gives up its pages, goes back to
+    the front of the queue, is recomputed later, and still produces exactly its own tokens."""
+    e = FakeEngine(num_pages=4, max_batch=2, budget=32)
+    pa, pb = list(range(1, 15)), list(range(20, 34))           # 14 tokens each: one page, 44 with the new ones
+    a, b = e.submit(pa, 30), e.submit(pb, 30)
+    e.run()
+    assert e.s.preemptions >= 1 and b.preemptions >= 1 and a.preemptions == 0
+    assert a.output == expected_output(pa, 30) and b.output == expected_output(pb, 30)
+    assert e.cache.free_pages() == [4]
+
+
+def test_no_admission_into_pages_the_live_requests_need_next():
+    """Three pages, the older request holds one: a newcomer whose prompt needs two would leave no
+    page to spare for the older one's growth, would be the newest, and so would lose its pages
+    again at once.  It waits in the queue instead; nobody is preempted."""
     e = FakeEngine(num_pages=3, max_batch=2, budget=32)
     pa, pb = list(range(1, 15)), list(range(20, 40))           # 14 tokens: one page; 20 tokens: two
     a, b = e.submit(pa, 12), e.submit(pb, 12)
+    e.step()
+    assert a.row == 0 and b.row == -1 and list(e.s.pending) == [b]
     e.run()
-    assert e.s.preemptions >= 1 and b.preemptions >= 1 and a.preemptions == 0
+    assert e.s.preemptions == 0
     assert a.output == expected_output(pa, 12) and b.output == expected_output(pb, 12)
     assert e.cache.free_pages() == [3]
 
@@ -238,14 +254,34 @@ def test_pages_run_out_newest_request_waits():
 
 
 def test_portion_shrinks_to_free_pages():
-    e = FakeEngine(num_pages=4, max_batch=2, budget=64)
-    a = e.submit(list(range(1, 40)), 4)                        # 39 tokens: 3 pages
-    e.step()
-    b = e.submit(list(range(1, 41)), 4)                        # would need 3, one is free
-    plan = e.s.plan()
-    got = {x.request is b: x.count for x in plan.entries}
-    assert got[False] == 1 and got[True] == 16                 # b takes what one page holds
-    assert plan.preempted == []
+    """The newest request is in the middle of its prompt when the older one has taken the last
+    free page: its next portion is cut to what its own last page still holds; nobody is preempted
+    (only a request admitted later may be)."""
+    e = FakeEngine(num_pages=4, max_batch=2, budget=12)
+    a = e.submit(list(range(1, 16)), 10)                       # 15 tokens, grows into a second page
+    b = e.submit(list(range(1, 41)), 4)                        # 40 tokens: three pages
+    shrunk = False
+    while e.s.has_work():
+        free_before = e.cache.free_pages()[0]
+        plan = e.s.plan()
+        assert plan is not None
+        for x in plan.entries:
+            left = x.request.sequence_len - x.request.cached
+            room = -x.request.cached % 16                  # slots left in the request's last page
+            if x.request is b and b.cached < 40 and free_before == 0 and left > room:
+                shrunk = True                              # it wanted more than its page holds and no page is free
+                assert x.count == room and plan.preempted == []
+        tokens = []
+        for x in plan.entries:
+            held = e.fed.setdefault(id(x.request), [])
+            held.extend(x.request.token_at(i) for i in range(x.start, x.start + x.count))
+            if x.samples:
+                tokens.append(next_token(held))
+        for r in plan.preempted:
+            e.fed.pop(id(r), None)
+        e.s.complete(plan, tokens)
+    assert shrunk
+    assert a.output == expected_output(list(range(1, 16)), 10) and b.output == expected_output(list(range(1, 41)), 4)
 
 
 @pytest.mark.parametrize("seed", range(5))
